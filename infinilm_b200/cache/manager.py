@@ -238,7 +238,7 @@ class CacheManager:
                 else:
                     # one slot more than are handed out: padding rows of a replayed step write there
                     shape = (self.slots.n_slots + 1,) + tuple(n.shape)
-                    dt = torch.float32 if n.dtype == "float32" else self.dtype
+                    dt = {"float32": torch.float32, "int32": torch.int32}.get(n.dtype, self.dtype)
                 grp.storage[i] = torch.zeros(shape, dtype=dt, device=self.device)
                 if n.kind == "paged_kv" and dt == torch.bfloat16 and self.kernel_page == 16:
                     from .. import ops

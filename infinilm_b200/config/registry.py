@@ -2,7 +2,7 @@
 
 Parity with InfiniLM: `csrc/models/models_registry.hpp:22-79` (static map from model_type to
 a model creator and a config creator), `csrc/models/model_factory.cpp:6-26` (unknown name is
-an `invalid_argument`). Lookup tries `architectures[0]`, then `model_type`.
+an `invalid_argument`). Lookup tries `architectures[0]`, then `architecture`, then `model_type`.
 """
 from __future__ import annotations
 
@@ -52,10 +52,12 @@ def lookup_architecture(raw: Dict[str, Any]) -> Architecture:
     archs = raw.get("architectures")
     if isinstance(archs, list) and archs:
         keys.append(str(archs[0]))
+    if isinstance(raw.get("architecture"), str):
+        keys.append(raw["architecture"])
     if raw.get("model_type") is not None:
         keys.append(str(raw["model_type"]))
     if not keys:
-        raise ConfigError("config.json: neither 'architectures' nor 'model_type' is given")
+        raise ConfigError("config.json: none of 'architectures', 'architecture' and 'model_type' is given")
     for k in keys:
         if k in _ARCHITECTURES:
             return _ARCHITECTURES[k]

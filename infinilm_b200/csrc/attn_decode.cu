@@ -72,7 +72,7 @@ constexpr int AD_MERGE_ROUND = 16;
 
 template <int WPR>
 __device__ __forceinline__ void ad_merge_row(float* fs, float* comb, const float* o_part, const float* ml_part, size_t row, int n_valid,
-                                             int n_splits, __nv_bfloat16* __restrict__ out, int lane, int sub) {
+                                             int n_splits, __nv_bfloat16* __restrict__ out, int lane, int sub, float sink_log2) {
     const size_t pr0 = row * n_splits;
     const int d_first = lane * 4;
     float4 v[AD_MERGE_ROUND];
@@ -103,6 +103,7 @@ __device__ __forceinline__ void ad_merge_row(float* fs, float* comb, const float
     }
     L = il_warp_sum(L);
     __syncwarp();
+    L += exp2f(sink_log2 - M);                    // the sink: one more key without a value (-inf: none, adds 0)
     const float inv = 1.f / L;
     for (int d = d_first; d < AT_HD; d += 128) {
         float4 acc = zero4;
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
     float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap kv_page_map,
-    int use_tma, int* __restrict__ status, __nv_bfloat16* __restrict__ out_direct) {
+    int use_tma, int* __restrict__ status, __nv_bfloat16* __restrict__ out_direct, const float* __restrict__ sink) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     // Lengths, block tables and the pages of earlier tokens do not come from the kernel before this one (it writes q and
@@ -426,6 +427,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
                 const float mw = sm_ml[(w * 16 + r) * 2];
                 L += ((mw == -INFINITY) ? 0.f : exp2f(mw - M)) * sm_ml[(w * 16 + r) * 2 + 1];
             }
+            if (sink) L += exp2f(sink[head0 + r] * 1.4426950408889634f - M);      // as the merge adds it
             const float inv = 1.f / L;
             const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
             *reinterpret_cast<uint2*>(out_direct + pr * AT_HD + d) = make_uint2(a, b);
@@ -451,13 +453,15 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
 template <int WPR>
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_part, const float* ml_part,
                                                                 const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
-                                                                int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
+                                                                int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out,
+                                                                const float* __restrict__ sink) {
     __shared__ float fs[4][AD_MAX_SPLITS];
     __shared__ __align__(16) float comb[WPR > 1 ? WPR * AT_HD : 4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * (4 / WPR) + warp / WPR;      // = e * nh + head
     // the lengths come with the step's descriptors, not from the kernel before: read them while that one still runs
     const int kvlen = row < n_rows ? entry_kvlen[row / nh] : 1;
+    const float sink_log2 = (sink && row < n_rows) ? sink[row % nh] * 1.4426950408889634f : -INFINITY;
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
     const int n_pages = (kvlen - 1) / AD_PAGE - lo / AD_PAGE + 1;
     if (pages_per_split <= 0) pages_per_split = (n_pages + n_splits - 1) / n_splits;
@@ -470,14 +474,14 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
             for (int d = lane * 4; d < AT_HD; d += 128) *reinterpret_cast<uint2*>(out + (size_t)row * AT_HD + d) = make_uint2(0u, 0u);
         return;
     }
-    ad_merge_row<WPR>(fs[warp], comb, o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane, warp % WPR);
+    ad_merge_row<WPR>(fs[warp], comb, o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane, warp % WPR, sink_log2);
 }
 
 // Launches the attention kernel and, for more than one split, the merge. Scratch: o_part float32 [n_decode*nh*n_splits*head_dim], ml_part [n_decode*nh*n_splits*2].
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
-                     int* status = nullptr) {
+                     int* status = nullptr, const float* sink = nullptr) {
     static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
     int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
     if (use_tma) {                                // a second map may follow the first: the page view (all zero: there is none)
@@ -499,7 +503,7 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
         scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status,
-        n_splits == 1 ? (__nv_bfloat16*)out : (__nv_bfloat16*)nullptr);
+        n_splits == 1 ? (__nv_bfloat16*)out : (__nv_bfloat16*)nullptr, sink);
     if (n_splits == 1) {                          // every row is final as the attention kernel leaves it: no merge
         IL_LAUNCH_CHECK();
         return IL_OK;
@@ -507,10 +511,10 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     const int n_rows = n_decode * nh;
     if (n_splits > AD_MERGE_WIDE_FROM) {
         IL_LAUNCH(attn_decode_merge_kernel<4>, n_rows, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window,
-                  pages_per_split, n_splits, (__nv_bfloat16*)out);
+                  pages_per_split, n_splits, (__nv_bfloat16*)out, sink);
     } else {
         IL_LAUNCH(attn_decode_merge_kernel<1>, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows,
-                  window, pages_per_split, n_splits, (__nv_bfloat16*)out);
+                  window, pages_per_split, n_splits, (__nv_bfloat16*)out, sink);
     }
     IL_LAUNCH_CHECK();
     return IL_OK;
@@ -538,13 +542,13 @@ IL_EXPORT int il_attn_decode_resident_blocks() {
 IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                              int bt_stride, const int* entry_kvlen, int page_size, int n_decode, int nh, int nkv, int hd,
                              float scale, int window, int pages_per_split, int n_splits, float* o_part, float* ml_part,
-                             const void* kv_map, int* status, cudaStream_t stream) {
+                             const void* kv_map, int* status, const float* sink, cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
-                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status);
+                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, sink);
 }
 
 // Writes two tensor maps (2 x 128 bytes at `out_maps`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16:

@@ -2,6 +2,8 @@
 // one with an online softmax in f32. It takes any mix of prompt portions and single decoded
 // tokens, any head size up to 256, any number of heads and groups, and an optional window.
 // It is the attention of the 32-bit path and the reference beside the fast bfloat16 kernels.
+// With `sink` (one f32 number per query head) the softmax's denominator also holds exp(sink[head]): a key without a
+// value whose score is the number itself, not multiplied by `scale`.
 //
 // The query of token t is at absolute position p = tok_pos[t] of its request and sees cache
 // positions max(0, p - window + 1) .. p (window <= 0: all). Query head j reads kv head j / (nh / nkv).
@@ -13,7 +15,7 @@ template <typename TA>
 __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA* __restrict__ out,
                                   const TA* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_entry, int page_size,
-                                  int nh, int nkv, int hd, float scale, int window) {
+                                  int nh, int nkv, int hd, float scale, int window, const float* __restrict__ sink) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j = blockIdx.y * (blockDim.x >> 5) + warp;
     const int t = blockIdx.x;
@@ -56,6 +58,7 @@ __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA
         m = mn;
     }
     TA* orow = out + (size_t)t * nh * hd + (size_t)j * hd;
+    if (sink) l += expf(sink[j] - m);             // (+inf when the sink towers over every score: the row is then zero)
     const float inv = 1.f / l;
 #pragma unroll
     for (int r = 0; r < AP_MAX_PER_LANE; ++r) {
@@ -67,7 +70,7 @@ __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA
 IL_EXPORT int il_attn_plain(const void* qkv, int act_kind, int row_stride, void* out, const void* cache,
                             const int* block_table, int bt_stride, const int* tok_pos, const int* tok_entry,
                             int page_size, int T, int nh, int nkv, int hd, float scale, int window,
-                            cudaStream_t stream) {
+                            const float* sink, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0) return IL_BAD_ARG;
     if (hd > 32 * AP_MAX_PER_LANE) return IL_UNSUPPORTED;
@@ -76,11 +79,11 @@ IL_EXPORT int il_attn_plain(const void* qkv, int act_kind, int row_stride, void*
     if (act_kind == IL_F32)
         attn_plain_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)qkv, row_stride, (float*)out, (const float*)cache,
                                                                   block_table, bt_stride, tok_pos, tok_entry, page_size, nh, nkv,
-                                                                  hd, scale, window);
+                                                                  hd, scale, window, sink);
     else if (act_kind == IL_BF16)
         attn_plain_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out,
                                                                           (const __nv_bfloat16*)cache, block_table, bt_stride, tok_pos,
-                                                                          tok_entry, page_size, nh, nkv, hd, scale, window);
+                                                                          tok_entry, page_size, nh, nkv, hd, scale, window, sink);
     else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

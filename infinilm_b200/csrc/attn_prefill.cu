@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
     const __nv_bfloat16* __restrict__ qkv, int row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ entry_qstart, const int* __restrict__ entry_kvlen, int first_entry, int n_entries, int nh,
-    int nkv, float scale_log2, int window, int tpt) {
+    int nkv, float scale_log2, int window, int tpt, const float* __restrict__ sink) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int G = nh / nkv;
     const int g = blockIdx.y;
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
     const size_t page_elems = (size_t)2 * nkv * AP_PAGE * AT_HD;
 
     // this thread's two rows: r0 = 16*warp + lane/4, r1 = r0 + 8
-    int rpos[2], rlo[2];
+    int rpos[2], rlo[2], rhead[2];
     bool rvalid[2];
     const __nv_bfloat16* qptr[2];
     __nv_bfloat16* optr[2];
@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
         rvalid[h] = r < rows_valid;
         const int tl = rvalid[h] ? r / G : 0, hh = rvalid[h] ? r - tl * G : 0;
         rpos[h] = start_pos + (tok0 - q0) + tl;
+        rhead[h] = g * G + hh;
         rlo[h] = (window > 0 && rpos[h] - window + 1 > 0) ? rpos[h] - window + 1 : 0;
         qptr[h] = rvalid[h] ? qkv + (size_t)(tok0 + tl) * row_stride + (size_t)(g * G + hh) * AT_HD : nullptr;
         optr[h] = rvalid[h] ? out + (size_t)(tok0 + tl) * nh * AT_HD + (size_t)(g * G + hh) * AT_HD : nullptr;
@@ -223,7 +224,8 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         if (!rvalid[h]) continue;
-        const float inv = 1.f / l[h];
+        // a sink joins the denominator as one more key without a value: 2^(sink * log2(e) - m), its score not scaled
+        const float inv = 1.f / (sink ? l[h] + ap_ex2(fmaf(sink[rhead[h]], 1.4426950408889634f, -m[h])) : l[h]);
         __nv_bfloat16* orow = optr[h];
 #pragma unroll
         for (int nt = 0; nt < AT_NT; ++nt) {
@@ -237,7 +239,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
 IL_EXPORT int il_attn_prefill(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                               int bt_stride, const int* entry_qstart, const int* entry_kvlen, int page_size,
                               int first_entry, int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale,
-                              int window, cudaStream_t stream) {
+                              int window, const float* sink, cudaStream_t stream) {
     if (n_tiles_total <= 0 || first_entry >= n_entries) return IL_OK;
     if (hd != HEAD_DIM || page_size != AP_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return IL_BAD_ARG;
@@ -252,7 +254,7 @@ IL_EXPORT int il_attn_prefill(const void* qkv, int row_stride, void* out, const 
     dim3 grid(n_tiles_total, nkv);
     attn_prefill_kernel<<<grid, AP_WARPS * 32, AP_SMEM, stream>>>(
         (const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, block_table, bt_stride,
-        entry_qstart, entry_kvlen, first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, AP_ROWS / G);
+        entry_qstart, entry_kvlen, first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, AP_ROWS / G, sink);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

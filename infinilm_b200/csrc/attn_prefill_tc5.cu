@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
     const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ qkv, int row_stride,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_qstart,
     const int* __restrict__ entry_kvlen, int first_entry, int n_entries, int nh, int nkv, float scale_log2, int window, int tpt,
-    int* __restrict__ status) {
+    int* __restrict__ status, const float* __restrict__ sink) {
     extern __shared__ __align__(1024) unsigned char smem[];
     if (t5_smem(smem) & 1023u) {                  // the swizzled tiles need 1 KB alignment; dynamic shared memory starts on it
         if (threadIdx.x == 0) atomicExch(status, 30);
@@ -337,6 +337,8 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
                 atomicExch(status, 38);
             } else {
                 t5_fence_after();
+                // a sink joins the denominator as one more key without a value: 2^(sink * log2(e) - m), its score not scaled
+                if (sink && rvalid) l += pt_ex2(fmaf(sink[g * G + hh], 1.4426950408889634f, -m));
                 const float inv = (l > 0.f) ? 1.f / l : 0.f;
                 // The rows go out through shared memory (Q's place: every product that reads Q is through): a thread owns a
                 // row of tensor memory, but 16-byte stores 8 KB apart cost a block 2 us; a warp's 32 rows are stored
@@ -389,7 +391,7 @@ IL_EXPORT int il_attn_prefill_tc5_rows() { return PT_ROWS; }
 IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, const void* kv_map, const int* block_table,
                                   int bt_stride, const int* entry_qstart, const int* entry_kvlen, int page_size, int first_entry,
                                   int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale, int window, int* status,
-                                  cudaStream_t stream) {
+                                  const float* sink, cudaStream_t stream) {
     if (n_tiles_total <= 0 || first_entry >= n_entries) return IL_OK;
     if (hd != HEAD_DIM || page_size != PT_PAGE || !kv_map || !status) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return IL_BAD_ARG;
@@ -411,7 +413,7 @@ IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, co
     dim3 grid(n_tiles_total, nkv);
     attn_prefill_tc5_kernel<<<grid, PT_THREADS, PT_SMEM, stream>>>(
         map, (const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, block_table, bt_stride, entry_qstart, entry_kvlen,
-        first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, PT_ROWS / G, status);
+        first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, PT_ROWS / G, status, sink);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

@@ -1,5 +1,5 @@
 // Residual add fused with RMSNorm.
-//   x = resid[r] + branch_scale * branch[r]   (branch may be absent)
+//   x = resid[r] + branch_scale * branch[r] + vec   (branch may be absent; vec, one f32 vector added to every row, too)
 //   resid[r] = x                              (kept in f32; skipped when a row list is given)
 //   out[i]  = x / sqrt(mean(x^2) + eps) * w
 // Sum of squares, rsqrt and the scaling are f32; one block per row with a fixed thread count,
@@ -9,7 +9,7 @@
 template <typename TA>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ branch, float bscale,
                                    const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ out,
-                                   const int* __restrict__ rows, int H) {
+                                   const int* __restrict__ rows, int H, const float* __restrict__ vec) {
     extern __shared__ float xs[];
     __shared__ float red[32];
     const int i = blockIdx.x;
@@ -20,9 +20,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         float x = rr[h];
         if (br) x += bscale * il_to_f(br[h]);
+        if (vec) x += vec[h];
         xs[h] = x;
         ss += x * x;
-        if (!rows && br) rr[h] = x;
+        if (!rows && (br || vec)) rr[h] = x;
     }
     ss = il_block_sum(ss, red);
     const float rstd = rsqrtf(ss / (float)H + eps);
@@ -51,7 +52,7 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
 template <typename TA, int MAXV>
 __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* resid, const TA* branch, float bscale,
                                                               const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ out,
-                                                              const int* __restrict__ rows, int H) {
+                                                              const int* __restrict__ rows, int H, const float* __restrict__ vec) {
     __shared__ float red[32];
     const int i = blockIdx.x;
     const int nv = H >> 2;                        // float4 groups in a row
@@ -87,10 +88,18 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* resid, cons
             x[k].w += bscale * b[k].w;
         }
     }
+    if (vec) {
+#pragma unroll
+        for (int k = 0; k < MAXV; ++k) {
+            const int v = threadIdx.x + k * 256;
+            const float4 a = v < nv ? ld4(vec + 4 * v) : make_float4(0.f, 0.f, 0.f, 0.f);
+            x[k].x += a.x, x[k].y += a.y, x[k].z += a.z, x[k].w += a.w;
+        }
+    }
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) ss += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
-    if (!rows && br) {
+    if (!rows && (br || vec)) {
 #pragma unroll
         for (int k = 0; k < MAXV; ++k) {
             const int v = threadIdx.x + k * 256;
@@ -109,25 +118,25 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* resid, cons
 
 template <typename TA>
 static int launch_vec(float* resid, const void* branch, float bscale, const void* w, int w_kind, float eps, void* out,
-                      const int* rows, int n_rows, int H, cudaStream_t stream) {
+                      const int* rows, int n_rows, int H, const float* vec, cudaStream_t stream) {
     const int nv = H >> 2;
     if (nv <= 256 * 2)
-        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 2>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 2>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec);
     else if (nv <= 256 * 4)
-        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 4>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 4>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec);
     else
-        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 8>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 8>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec);
     return 0;
 }
 
 IL_EXPORT int il_add_rmsnorm(float* resid, const void* branch, float bscale, const void* w, int w_kind,
                              float eps, void* out, int act_kind, const int* rows, int n_rows, int H,
-                             cudaStream_t stream) {
+                             const float* vec, cudaStream_t stream) {
     if (n_rows <= 0) return IL_OK;
     if (H <= 0) return IL_BAD_ARG;
     if (H % 4 == 0 && H <= 256 * 8 * 4 && (act_kind == IL_F32 || act_kind == IL_BF16)) {
-        if (act_kind == IL_F32) launch_vec<float>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, stream);
-        else launch_vec<__nv_bfloat16>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, stream);
+        if (act_kind == IL_F32) launch_vec<float>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, vec, stream);
+        else launch_vec<__nv_bfloat16>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, vec, stream);
         IL_LAUNCH_CHECK();
         return IL_OK;
     }
@@ -136,10 +145,10 @@ IL_EXPORT int il_add_rmsnorm(float* resid, const void* branch, float bscale, con
     const int threads = 256;
     if (act_kind == IL_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(resid, (const float*)branch, bscale, w, w_kind, eps, (float*)out, rows, H);
+        add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(resid, (const float*)branch, bscale, w, w_kind, eps, (float*)out, rows, H, vec);
     } else if (act_kind == IL_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(resid, (const __nv_bfloat16*)branch, bscale, w, w_kind, eps, (__nv_bfloat16*)out, rows, H);
+        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(resid, (const __nv_bfloat16*)branch, bscale, w, w_kind, eps, (__nv_bfloat16*)out, rows, H, vec);
     } else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

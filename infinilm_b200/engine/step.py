@@ -421,8 +421,10 @@ class StepRunner:
             lengths_are_bounds=graph_key is not None)
 
         caches = []
-        for i, st in enumerate(self.model.order):
-            owner = i if st.cache_from is None else st.cache_from
+        owners = [i if st.cache_from is None else st.cache_from for i, st in enumerate(self.model.order)]
+        if self.model.embedding_cache_index is not None:      # what the embedding keeps of a request comes last
+            owners.append(self.model.embedding_cache_index)
+        for i, owner in enumerate(owners):
             g = self.cache.group_of_entry.get(owner)
             if g is None:
                 caches.append(None)

@@ -5,7 +5,7 @@ import importlib
 
 from .causal_lm import CausalLM
 
-BUILTIN = ("minicpm4",)
+BUILTIN = ("minicpm4", "nirozen")
 
 
 def register_builtin() -> None:

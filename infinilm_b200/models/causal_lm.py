@@ -22,13 +22,21 @@ class CausalLM:
         self.blocks = []
         for ls in spec.layers:
             arr = part_class("arrangement", ls.arrangement)
+            if (ls.ffn is None) != (ls.ffn_norm is None):
+                raise ValueError("a layer has a feed-forward and its norm, or neither")
             self.blocks.append(arr(build_part("norm", ls.mixer_norm, dtype), build_part("mixer", ls.mixer, dtype),
-                                   build_part("norm", ls.ffn_norm, dtype), build_part("feed_forward", ls.ffn, dtype),
-                                   ls.params))
+                                   None if ls.ffn_norm is None else build_part("norm", ls.ffn_norm, dtype),
+                                   None if ls.ffn is None else build_part("feed_forward", ls.ffn, dtype), ls.params))
         self.final_norm = build_part("norm", spec.final_norm, dtype)
         self.head = build_part("head", spec.head, dtype)
         self.order = list(spec.order)
+        self.pass_vectors = None if spec.pass_vectors is None else build_part("embedding", spec.pass_vectors, dtype)
         for i, st in enumerate(self.order):
+            if st.add_row is not None:
+                if self.pass_vectors is None or not 0 <= st.add_row < self.pass_vectors.rows:
+                    raise ValueError(f"run order entry {i} adds row {st.add_row} of a table the model does not have")
+                if not self.blocks[st.layer].takes_pre_add:
+                    raise ValueError(f"run order entry {i}: its block's arrangement cannot add a vector first")
             if not 0 <= st.layer < len(self.blocks):
                 raise ValueError(f"run order entry {i} names layer {st.layer}, which does not exist")
             if st.cache_from is not None and not (0 <= st.cache_from < i and self.order[st.cache_from].cache_from is None):
@@ -43,6 +51,8 @@ class CausalLM:
         out: List[Part] = [self.embedding]
         for b in self.blocks:
             out.extend(b.parts())
+        if self.pass_vectors is not None:
+            out.append(self.pass_vectors)
         out += [self.final_norm, self.head]
         return out
 
@@ -51,11 +61,19 @@ class CausalLM:
 
     # -- cache -----------------------------------------------------------------------------
     def cache_needs(self) -> List[Optional[CacheNeed]]:
-        """One entry per run-order entry: what it keeps (None: nothing, or it reads another's)."""
+        """One entry per run-order entry: what it keeps (None: nothing, or it reads another's); then one more for the
+        embedding, if that keeps something of a request between steps (`embedding_cache_index`)."""
         needs = []
         for st in self.order:
             needs.append(None if st.cache_from is not None else self.blocks[st.layer].mixer.cache_need())
+        if self.embedding_cache_index is not None:
+            needs.append(self.embedding.cache_need())
         return needs
+
+    @property
+    def embedding_cache_index(self) -> Optional[int]:
+        need = getattr(self.embedding, "cache_need", None)
+        return len(self.order) if need is not None and need() is not None else None
 
     # -- forward ---------------------------------------------------------------------------
     def forward(self, ctx, caches) -> torch.Tensor:
@@ -63,16 +81,22 @@ class CausalLM:
         `caches[i]` is the cache view of run-order entry i."""
         T = ctx.T
         resid = ctx.ws.rows("resid", T, self.hidden, torch.float32)
-        self.embedding.forward(ctx.token_ids, resid)
+        if getattr(self.embedding, "takes_context", False):    # an embedding that reads positions or keeps state
+            ec = self.embedding_cache_index
+            self.embedding.forward(ctx.token_ids, resid, ctx, caches[ec] if ec is not None else None)
+        else:
+            self.embedding.forward(ctx.token_ids, resid)
         pending = None
         for i, st in enumerate(self.order):
             # the block that runs next may take its first norm half done (its weights applied, the rms still to divide by)
             blk = self.blocks[st.layer]
-            nxt = self.blocks[self.order[i + 1].layer] if i + 1 < len(self.order) else None
+            nxt_st = self.order[i + 1] if i + 1 < len(self.order) else None
+            nxt = self.blocks[nxt_st.layer] if nxt_st is not None and nxt_st.add_row is None else None
+            kw = {} if st.add_row is None else {"pre_add": self.pass_vectors.row(st.add_row)}
             if blk.takes_next_norm and nxt is not None and nxt.accepts_normed_input(T):
-                pending = blk.run(resid, pending, ctx, caches[i], next_norm=nxt.mixer_norm)
+                pending = blk.run(resid, pending, ctx, caches[i], next_norm=nxt.mixer_norm, **kw)
             else:
-                pending = blk.run(resid, pending, ctx, caches[i])
+                pending = blk.run(resid, pending, ctx, caches[i], **kw)
             if ctx.tap is not None:
                 ctx.tap(f"layer{i}", resid, pending)
         n = ctx.n_want

@@ -126,12 +126,14 @@ def patch_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src_idx: torch.Ten
 
 
 def add_rmsnorm(resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scale: float, weight: torch.Tensor,
-                eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-    """resid += branch_scale * branch (f32, in place); out = RMSNorm(resid) * weight.
+                eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None, vec: Optional[torch.Tensor] = None) -> None:
+    """resid += branch_scale * branch (+ vec, one float32 vector for every row) (f32, in place); out = RMSNorm(resid) * weight.
 
     With `rows` (int32 indices) only those rows are normalised, into out[0..len(rows)), and
     `resid` is left as it was."""
-    _need_cuda(resid, branch, weight, out, rows)
+    _need_cuda(resid, branch, weight, out, rows, vec)
+    if vec is not None and (vec.dtype != torch.float32 or vec.numel() != resid.shape[1] or not vec.is_contiguous()):
+        raise KernelError("add_rmsnorm: vec must be a contiguous float32 [H]")
     T, H = resid.shape
     n = T if rows is None else rows.numel()
     if resid.dtype != torch.float32 or weight.numel() != H or out.shape[-1] != H or out.shape[0] < n:
@@ -144,9 +146,9 @@ def add_rmsnorm(resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scal
     if branch is not None:
         _contig("branch", branch)
     f = _fn("rmsnorm", "il_add_rmsnorm", [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_float, _c_void_p,
-                                          _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+                                          _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p])
     _check(f(_ptr(resid), _ptr(branch), branch_scale, _ptr(weight), kind_of(weight.dtype), eps, _ptr(out),
-             kind_of(out.dtype), _ptr(rows), n, H, _stream()), "add_rmsnorm")
+             kind_of(out.dtype), _ptr(rows), n, H, _ptr(vec), _stream()), "add_rmsnorm")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -195,9 +197,13 @@ def rope_store(qkv: torch.Tensor, tok_pos: torch.Tensor, tok_entry: torch.Tensor
 
 def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                     tok_pos: torch.Tensor, tok_entry: torch.Tensor, page_size: int, n_heads: int,
-                    n_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None) -> None:
-    """Causal attention of every token of `qkv` over its request's cache pages (plain kernel)."""
-    _need_cuda(qkv, out, cache, block_table, tok_pos, tok_entry)
+                    n_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None,
+                    sink: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of every token of `qkv` over its request's cache pages (plain kernel). `qkv` needs the query
+    heads only (keys and values are read from the cache). `sink`: float32 [heads], a score per head that joins the
+    softmax's denominator without a value."""
+    _need_cuda(qkv, out, cache, block_table, tok_pos, tok_entry, sink)
+    _check_sink(sink, n_heads)
     T = qkv.shape[0]
     if out.shape != (T, n_heads * head_dim) or out.dtype != qkv.dtype or cache.dtype != qkv.dtype:
         raise KernelError("attention_plain: out [T, heads*head_dim], same dtype as qkv and cache")
@@ -206,10 +212,15 @@ def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_plain", "il_attn_plain", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                            _c_int, _c_void_p])
+                                            _c_int, _c_void_p, _c_void_p])
     _check(f(_ptr(qkv), kind_of(qkv.dtype), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table),
              block_table.shape[1], _ptr(tok_pos), _ptr(tok_entry), page_size, T, n_heads, n_kv_heads, head_dim,
-             scale, int(window or 0), _stream()), "attention_plain")
+             scale, int(window or 0), _ptr(sink), _stream()), "attention_plain")
+
+
+def _check_sink(sink: Optional[torch.Tensor], n_heads: int) -> None:
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
+        raise KernelError("attention: sink must be a contiguous float32 tensor, one number per query head")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
@@ -262,13 +273,15 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Opt
 def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      entry_kvlen: torch.Tensor, n_decode: int, page_size: int, n_heads: int, n_kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
-                     o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None) -> None:
+                     o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None,
+                     sink: Optional[torch.Tensor] = None) -> None:
     """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each), then the merge of
     the splits (a second launch; with n_splits = 1 there is none and the attention kernel writes `out` itself). A row whose length is 0 gets zeros; a block-table entry below 0 is never followed.
     pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
     kv_map: the cache's tensor map from `kv_tensor_map` (pages then come in by TMA tensor copies).
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
-    _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part)
+    _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part, sink)
+    _check_sink(sink, n_heads)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 tensors")
     if o_part is None or ml_part is None or o_part.dtype != torch.float32 or ml_part.dtype != torch.float32:
@@ -283,13 +296,13 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_decode", "il_attn_decode", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                               _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p,
-                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
     if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != KV_MAP_BYTES):
         raise KernelError("attention_decode: kv_map must be the host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
-             _stream()), "attention_decode")
+             _ptr(sink), _stream()), "attention_decode")
     if n_splits > 1:
         count_launches(1)                         # the merge kernel (a single split needs none: the attention kernel finishes the rows)
 
@@ -333,10 +346,11 @@ def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       entry_qstart: torch.Tensor, entry_kvlen: torch.Tensor, first_entry: int, n_entries: int,
                       n_tiles_total: int, page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                      window: Optional[int]) -> None:
+                      window: Optional[int], sink: Optional[torch.Tensor] = None) -> None:
     """bfloat16 causal attention of the tokens of entries [first_entry, n_entries) over their cache pages.
     n_tiles_total = sum over those entries of ceil(q_len / (64 // (heads/kv_heads)))."""
-    _need_cuda(qkv, out, cache, block_table, entry_qstart, entry_kvlen)
+    _need_cuda(qkv, out, cache, block_table, entry_qstart, entry_kvlen, sink)
+    _check_sink(sink, n_heads)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: bfloat16 tensors")
     if out.shape != (qkv.shape[0], n_heads * head_dim):
@@ -344,10 +358,10 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_prefill", "il_attn_prefill", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                                                 _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                                _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
+                                                _c_int, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_qstart),
              _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads, head_dim, scale,
-             int(window or 0), _stream()), "attention_prefill")
+             int(window or 0), _ptr(sink), _stream()), "attention_prefill")
 
 
 _tc5_prefill_rows = {}
@@ -385,10 +399,11 @@ def _has_third_map(kv_map: torch.Tensor) -> bool:
 def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Tensor, block_table: torch.Tensor,
                           entry_qstart: torch.Tensor, entry_kvlen: torch.Tensor, first_entry: int, n_entries: int,
                           n_tiles_total: int, page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                          window: Optional[int]) -> None:
+                          window: Optional[int], sink: Optional[torch.Tensor] = None) -> None:
     """The same attention as `attention_prefill`, on tcgen05 tensor cores with tensor memory; `kv_map` is the cache's
     tensor map (`kv_tensor_map`). n_tiles_total = sum over the entries of ceil(q_len / (prefill_tc5_rows(head_dim) // (heads/kv_heads)))."""
-    _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen)
+    _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen, sink)
+    _check_sink(sink, n_heads)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc5: bfloat16 tensors")
     if not _has_third_map(kv_map):
@@ -398,10 +413,10 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
     _contig("qkv", qkv), _contig("out", out), _contig("block_table", block_table)
     f = _fn("attn_prefill_tc5", "il_attn_prefill_tc5",
             [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+             _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _c_void_p(kv_map.data_ptr() + 256), _ptr(block_table), block_table.shape[1],
              _ptr(entry_qstart), _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads,
-             head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _stream()), "attention_prefill_tc5")
+             head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _ptr(sink), _stream()), "attention_prefill_tc5")
 
 
 SKINNY_MAX_ROWS = 16
@@ -621,6 +636,166 @@ def gemm_mid(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float =
                                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
              M, N, K, int(glu), nb, bm, _ptr(stream_status(x.device)), _stream()), "gemm_mid")
+
+
+_c_ll = ctypes.c_longlong
+
+
+def embed_pair_pos(ids: torch.Tensor, tok_pos: torch.Tensor, tok_entry: torch.Tensor, entry_qstart: torch.Tensor, table: torch.Tensor,
+                   scale: float, pair_table: Optional[torch.Tensor], buckets: int, mul_prev: int, mul_cur: int,
+                   prev_state: Optional[torch.Tensor], read_slots: Optional[torch.Tensor], write_slots: Optional[torch.Tensor],
+                   inv_freq: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t,:] (f32) = table[ids[t]] * scale + pair_table[(prev * mul_prev + ids[t] * mul_cur) mod buckets] (row `buckets`
+    at position 0) + sinusoid(tok_pos[t]) (entry 2i: sin(pos * inv_freq[i]), 2i+1: cos). The previous token of an entry's
+    first token is `prev_state[read_slots[entry]] - 1`; the entry's last token + 1 goes to `prev_state[write_slots[entry]]`."""
+    _need_cuda(ids, tok_pos, tok_entry, entry_qstart, table, pair_table, prev_state, read_slots, write_slots, inv_freq, out)
+    T, (V, H) = ids.numel(), table.shape
+    if out.dtype != torch.float32 or out.shape != (T, H):
+        raise KernelError("embed_pair_pos: out float32 [T,H]")
+    for t in (ids, tok_pos, tok_entry, entry_qstart, prev_state, read_slots, write_slots):
+        if t is not None and t.dtype != torch.int32:
+            raise KernelError("embed_pair_pos: descriptors and the state are int32")
+    if pair_table is not None and (pair_table.dtype != table.dtype or tuple(pair_table.shape) != (buckets + 1, H)):
+        raise KernelError("embed_pair_pos: pair_table [buckets + 1, H] of the table's dtype")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != (H + 1) // 2):
+        raise KernelError("embed_pair_pos: inv_freq float32 [ceil(H/2)]")
+    _contig("table", table), _contig("out", out)
+    if pair_table is not None:
+        _contig("pair_table", pair_table)
+    f = _fn("embedding", "il_embed_pair_pos", [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
+                                               _c_ll, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                               _c_int, _c_void_p])
+    _check(f(_ptr(ids), _ptr(tok_pos), _ptr(tok_entry), _ptr(entry_qstart), _ptr(table), kind_of(table.dtype), scale, _ptr(pair_table),
+             int(buckets), int(mul_prev), int(mul_cur), _ptr(prev_state), _ptr(read_slots), _ptr(write_slots), _ptr(inv_freq),
+             _ptr(out), T, H, V, _stream()), "embed_pair_pos")
+
+
+def latent_norm_store(proj: torch.Tensor, off_a: int, n_a: int, off_b: int, n_b: int, w_a: Optional[torch.Tensor],
+                      w_b: torch.Tensor, eps: float, out_a: Optional[torch.Tensor], out_b: Optional[torch.Tensor],
+                      tok_pos: torch.Tensor, tok_entry: torch.Tensor, block_table: torch.Tensor, cache: Optional[torch.Tensor],
+                      page_size: int) -> None:
+    """Per row of `proj`: columns [off_a, off_a + n_a) and [off_b, off_b + n_b) are each divided by their root mean
+    square (f32) and multiplied by `w_a` / `w_b`. The first goes to `out_a` [T, n_a]; the second to `out_b` (if given) and
+    into the token's slot of `cache` [pages, 2, 1, page, n_b], K plane and V plane alike."""
+    _need_cuda(proj, w_a, w_b, out_a, out_b, tok_pos, tok_entry, block_table, cache)
+    T = proj.shape[0]
+    if proj.stride(1) != 1 or off_a + n_a > proj.shape[1] or off_b + n_b > proj.shape[1]:
+        raise KernelError("latent_norm_store: segments lie outside the rows")
+    if n_a and (w_a is None or w_a.numel() != n_a or out_a is None or tuple(out_a.shape) != (T, n_a) or out_a.dtype != proj.dtype):
+        raise KernelError("latent_norm_store: w_a [n_a], out_a [T, n_a] of proj's dtype")
+    if w_b.numel() != n_b or (n_a and w_a.dtype != w_b.dtype):
+        raise KernelError("latent_norm_store: w_b [n_b], of w_a's dtype")
+    if out_b is not None and (tuple(out_b.shape) != (T, n_b) or out_b.dtype != proj.dtype or not out_b.is_contiguous()):
+        raise KernelError("latent_norm_store: out_b [T, n_b] of proj's dtype")
+    if tok_pos.dtype != torch.int32 or tok_entry.dtype != torch.int32 or block_table.dtype != torch.int32:
+        raise KernelError("latent_norm_store: descriptors must be int32")
+    _contig("block_table", block_table)
+    if cache is not None:
+        _contig("cache", cache)
+        if cache.dtype != proj.dtype or tuple(cache.shape[1:]) != (2, 1, page_size, n_b):
+            raise KernelError("latent_norm_store: cache [pages,2,1,page,n_b] of proj's dtype")
+    f = _fn("latent", "il_latent_norm_store", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
+                                               _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
+                                               _c_int, _c_void_p])
+    _check(f(_ptr(proj), kind_of(proj.dtype), proj.stride(0), off_a, n_a, off_b, n_b, _ptr(w_a), _ptr(w_b), kind_of(w_b.dtype), eps,
+             _ptr(out_a), _ptr(out_b), _ptr(tok_pos), _ptr(tok_entry), _ptr(block_table), block_table.shape[1], _ptr(cache), page_size,
+             T, _stream()), "latent_norm_store")
+
+
+MOE_MAX_TOP = 32
+
+
+def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int) -> None:
+    """Per row of x [T,H]: logits = x w^T + bias in f32, the `top` largest experts into idx [T, top] (int32), the softmax
+    over the chosen logits into wt [T, top] (float32)."""
+    _need_cuda(x, w, bias, idx, wt)
+    T, H = x.shape
+    E = w.shape[0]
+    if w.dtype != x.dtype or w.shape[1] != H or x.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError("moe_route: x [T,H], w [E,H] of the same dtype")
+    if idx.dtype != torch.int32 or wt.dtype != torch.float32 or tuple(idx.shape) != (T, top) or tuple(wt.shape) != (T, top):
+        raise KernelError("moe_route: idx int32 [T, top], wt float32 [T, top]")
+    if not 0 < top <= min(E, MOE_MAX_TOP):
+        raise KernelError(f"moe_route: top must be in 1..min(experts, {MOE_MAX_TOP})")
+    if bias is not None and bias.numel() != E:
+        raise KernelError("moe_route: bias [E]")
+    _contig("idx", idx), _contig("wt", wt)
+    f = _fn("moe", "il_moe_route", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                                    _c_int, _c_void_p])
+    _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), _ptr(w), _ptr(bias), kind_of(bias.dtype) if bias is not None else 0, _ptr(idx),
+             _ptr(wt), T, H, E, top, _stream()), "moe_route")
+
+
+def moe_sort(idx: torch.Tensor, n_experts: int, group_off: torch.Tensor, pos_of_slot: torch.Tensor, row_of_pos: torch.Tensor) -> None:
+    """Orders the slots (token, choice) of idx [T, top] by expert: group_off [E + 1], pos_of_slot [T * top], row_of_pos [T * top]."""
+    _need_cuda(idx, group_off, pos_of_slot, row_of_pos)
+    T, top = idx.shape
+    for t in (idx, group_off, pos_of_slot, row_of_pos):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("moe_sort: contiguous int32 tensors")
+    if group_off.numel() < n_experts + 1 or pos_of_slot.numel() < T * top or row_of_pos.numel() < T * top:
+        raise KernelError("moe_sort: outputs too small")
+    f = _fn("moe", "il_moe_sort", [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p])
+    _check(f(_ptr(idx), T * top, top, n_experts, _ptr(group_off), _ptr(pos_of_slot), _ptr(row_of_pos), _stream()), "moe_sort")
+
+
+def moe_combine(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, shared_rows: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t] = sum_k wt[t,k] * y[pos_of_slot[t*top + k]] (+ shared_rows[t]), summed in f32 in the order of k."""
+    _need_cuda(y, pos_of_slot, wt, shared_rows, out)
+    T, top = wt.shape
+    H = out.shape[1]
+    if y.dtype != out.dtype or y.shape[1] != H or out.shape[0] != T or y.shape[0] < T * top:
+        raise KernelError("moe_combine: y [T * top, H], out [T, H] of the same dtype")
+    if shared_rows is not None and (shared_rows.dtype != out.dtype or tuple(shared_rows.shape) != (T, H)):
+        raise KernelError("moe_combine: shared_rows [T, H]")
+    _contig("y", y), _contig("out", out), _contig("wt", wt)
+    if shared_rows is not None:
+        _contig("shared_rows", shared_rows)
+    f = _fn("moe", "il_moe_combine", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(y), kind_of(y.dtype), _ptr(pos_of_slot), _ptr(wt), _ptr(shared_rows), _ptr(out), T, H, top, _stream()), "moe_combine")
+
+
+def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, group_off: Optional[torch.Tensor] = None,
+                 a_rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None, glu: bool = False,
+                 gate: Optional[torch.Tensor] = None) -> None:
+    """Products over groups, out_g = a_g w_g^T, w [G, N, K] (glu: [G, 2N, K], gate rows then up rows, out = silu(gate) * up).
+    Ragged (`group_off` int32 [G + 1] on the device): the `n_rows` rows of `out` [n_rows, N] stand sorted by group, group g
+    owning places group_off[g] .. group_off[g+1] - 1; the row of `a` [*, K] at a place is a_rows[place] (or the place).
+    Batched (no `group_off`): a [M, G, K] and out [M, G, N] are column ranges of shared rows; `gate` [M, G, N] multiplies
+    out by its sigmoid."""
+    _need_cuda(a, w, out, group_off, a_rows, gate)
+    if w.dim() != 3 or not w.is_contiguous() or w.dtype != a.dtype or out.dtype != a.dtype:
+        raise KernelError("gemm_grouped: w [G, N, K] contiguous, one dtype for a, w and out")
+    G, K = w.shape[0], w.shape[2]
+    N = w.shape[1] // 2 if glu else w.shape[1]
+    if group_off is not None:
+        M = int(n_rows if n_rows is not None else out.shape[0])
+        if a.dim() != 2 or a.shape[1] != K or a.stride(1) != 1 or out.dim() != 2 or out.shape[1] != N or out.shape[0] < M or out.stride(1) != 1:
+            raise KernelError(f"gemm_grouped: ragged a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+        if group_off.dtype != torch.int32 or group_off.numel() < G + 1 or (a_rows is not None and (a_rows.dtype != torch.int32 or a_rows.numel() < M)):
+            raise KernelError("gemm_grouped: group_off int32 [G + 1], a_rows int32 [rows]")
+        if a_rows is None and a.shape[0] < M:
+            raise KernelError("gemm_grouped: a has fewer rows than places")
+        if gate is not None:
+            raise KernelError("gemm_grouped: gate goes with the batched form")
+        lda, a_gs, ldc, c_gs, ldg, g_gs = a.stride(0), 0, out.stride(0), 0, 0, 0
+    else:
+        if a.dim() != 3 or out.dim() != 3 or a.shape[1] != G or out.shape[1] != G or a.shape[2] != K or out.shape[2] != N or a.shape[0] != out.shape[0]:
+            raise KernelError(f"gemm_grouped: batched a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+        if a.stride(2) != 1 or out.stride(2) != 1:
+            raise KernelError("gemm_grouped: innermost dimension must be contiguous")
+        M = a.shape[0]
+        lda, a_gs, ldc, c_gs = a.stride(0), a.stride(1), out.stride(0), out.stride(1)
+        ldg = g_gs = 0
+        if gate is not None:
+            if tuple(gate.shape) != tuple(out.shape) or gate.dtype != out.dtype or gate.stride(2) != 1:
+                raise KernelError("gemm_grouped: gate [M, G, N] of out's dtype")
+            ldg, g_gs = gate.stride(0), gate.stride(1)
+    f = _fn("gemm_grouped", "il_gemm_grouped", [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p, _c_int,
+                                                _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_ll,
+                                                _c_void_p])
+    _check(f(_ptr(a), kind_of(a.dtype), lda, a_gs, _ptr(a_rows), _ptr(w), w.stride(1), w.stride(0), _ptr(out), ldc, c_gs, _ptr(group_off),
+             G, M, N, K, int(glu), _ptr(gate), ldg, g_gs, _stream()), "gemm_grouped")
 
 
 # ----------------------------------------------------------------------------------------------

@@ -21,6 +21,78 @@ from .linear import Linear
 from .spec import CacheNeed, PartSpec, WeightSpec
 
 
+class PagedAttend:
+    """Causal attention of a step's rows over the paged cache, by the kernel that fits each part of the step: what an
+    attention mixer of any kind calls once its queries stand in rows and its keys and values in the cache.
+    `sink`: float32 [heads] on the device or None - a score per head that joins the softmax's denominator without a value."""
+
+    # The fast bfloat16 kernels take kernel pages of 16 keys (the cache manager lays larger pages out as runs of them)
+    # and at most 64 query heads per kv head; anything else, and the whole float32 path, runs the plain kernel.
+    FAST_PAGE = 16
+    FAST_MAX_GROUP = 64
+    _warned_plain = False
+
+    WAVE_FILL = 2.0 / 3.0                         # share of the blocks the device holds at once that the splits aim at
+
+    def __init__(self, dtype, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None,
+                 force_plain: bool = False, prefill_kernel: str = "auto"):
+        self.dtype, self.nh, self.nkv, self.hd, self.scale, self.window = dtype, n_heads, n_kv_heads, head_dim, scale, window
+        self.force_plain, self.prefill_kernel = force_plain, prefill_kernel
+        self.sink: Optional[torch.Tensor] = None
+
+    def fast_ok(self, page_size: int) -> bool:
+        return (self.dtype == torch.bfloat16 and page_size == self.FAST_PAGE and self.nh // self.nkv <= self.FAST_MAX_GROUP
+                and not self.force_plain and self.hd % 16 == 0 and 16 <= self.hd <= 256)
+
+    def decode_splits(self, base: int, max_pages: int, resident: int) -> int:
+        """Splits of the keys for `base` blocks per split: as many as fill the wanted share of one wave of blocks
+        (`resident`: what the device runs at once, from the occupancy query), never more - a second, part-filled wave
+        costs more in partials than it gains - and at least four pages a split."""
+        target = max(1, int(resident * self.WAVE_FILL))
+        return max(1, min(target // base, (max_pages + 3) // 4, 128))
+
+    def run(self, qkv, out, ctx, cache) -> None:
+        G = self.nh // self.nkv
+        if not self.fast_ok(cache.page_size):
+            if self.dtype == torch.bfloat16 and not self.force_plain and not PagedAttend._warned_plain:
+                PagedAttend._warned_plain = True
+                warnings.warn(f"attention: pages of {cache.page_size} keys / {G} query heads per kv head / head size {self.hd} are outside "
+                              f"the fast bfloat16 kernels (pages of 16 or a multiple, at most {self.FAST_MAX_GROUP} heads per kv head, "
+                              "head sizes in steps of 16 up to 256): the plain kernel runs, at a fraction of their speed",
+                              RuntimeWarning, stacklevel=2)
+            ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
+                                cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window, self.sink)
+            return
+        n_dec, E = ctx.n_decode, ctx.n_entries
+        if n_dec > 0:
+            max_len = max(ctx.h_kvlen[:n_dec])
+            if self.window is not None:
+                max_len = min(max_len, self.window + self.FAST_PAGE)
+            max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
+            base = n_dec * self.nkv * ((G + 15) // 16)
+            n_splits = self.decode_splits(base, max_pages, ops.attention_decode_resident_blocks(self.hd))
+            rows = n_dec * self.nh * n_splits
+            ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
+                                 self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
+                                 ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
+                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map, sink=self.sink)
+        if E > n_dec:
+            # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128) and the cache
+            # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.
+            tc5 = (self.prefill_kernel != "mma" and cache.tma_map is not None
+                   and ops.prefill_tc5_ok(self.hd, G, cache.page_size, cache.tma_map))
+            tpt = max(1, (ops.prefill_tc5_rows(self.hd) if tc5 else 64) // G)
+            n_tiles = ctx.prompt_tiles(tpt)
+            if tc5:
+                ops.attention_prefill_tc5(qkv, out, cache.tma_map, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
+                                          n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
+                                          self.window, sink=self.sink)
+            else:
+                ops.attention_prefill(qkv, out, cache.storage, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
+                                      n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
+                                      self.window, sink=self.sink)
+
+
 class Attention(Mixer):
     """params: hidden, n_heads, n_kv_heads, head_dim, qkv_bias, out_bias, out_scale,
     window (None = all keys), position (PartSpec of a position encoding)."""
@@ -39,6 +111,7 @@ class Attention(Mixer):
         self.prefill_kernel = str(p.get("prefill_kernel", os.environ.get("INFINILM_B200_PREFILL_ATTN", "auto")))   # "mma": never tcgen05
         self.fuse_rope = os.environ.get("INFINILM_B200_FUSE_ROPE", "1") != "0"
         self.scale = 1.0 / math.sqrt(self.hd)
+        self.core = PagedAttend(dtype, self.nh, self.nkv, self.hd, self.scale, self.window, self.force_plain, self.prefill_kernel)
         self.n_qkv = (self.nh + 2 * self.nkv) * self.hd
         self.qkv = Linear(self.hidden, self.n_qkv, dtype)
         self.o_proj = Linear(self.nh * self.hd, self.hidden, dtype, alpha=float(p.get("out_scale", 1.0)))
@@ -109,61 +182,13 @@ class Attention(Mixer):
                                          ctx.ws.rows("sumsq_mixer", T, (self.hidden + 15) // 16, torch.float32))
         return self.o_proj(out, ctx.ws.rows("branch", T, self.hidden, self.dtype))
 
-    # The fast bfloat16 kernels take kernel pages of 16 keys (the cache manager lays larger pages out as runs of them)
-    # and at most 64 query heads per kv head; anything else, and the whole float32 path, runs the plain kernel.
-    FAST_PAGE = 16
-    FAST_MAX_GROUP = 64
-    _warned_plain = False
-
-    WAVE_FILL = 2.0 / 3.0                         # share of the blocks the device holds at once that the splits aim at
+    def attend(self, qkv, out, ctx, cache) -> None:
+        self.core.run(qkv, out, ctx, cache)
 
     def decode_splits(self, base: int, max_pages: int, resident: int) -> int:
-        """Splits of the keys for `base` blocks per split: as many as fill the wanted share of one wave of blocks
-        (`resident`: what the device runs at once, from the occupancy query), never more - a second, part-filled wave
-        costs more in partials than it gains - and at least four pages a split."""
-        target = max(1, int(resident * self.WAVE_FILL))
-        return max(1, min(target // base, (max_pages + 3) // 4, 128))
+        return self.core.decode_splits(base, max_pages, resident)
 
-    def attend(self, qkv, out, ctx, cache) -> None:
-        G = self.nh // self.nkv
-        if (self.dtype != torch.bfloat16 or cache.page_size != self.FAST_PAGE or G > self.FAST_MAX_GROUP
-                or self.force_plain):
-            if self.dtype == torch.bfloat16 and not self.force_plain and not Attention._warned_plain:
-                Attention._warned_plain = True
-                warnings.warn(f"attention: pages of {cache.page_size} keys / {G} query heads per kv head are outside the fast "
-                              f"bfloat16 kernels (pages of 16 or a multiple, at most {self.FAST_MAX_GROUP} heads per kv head): "
-                              "the plain kernel runs, at a fraction of their speed", RuntimeWarning, stacklevel=2)
-            ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
-                                cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window)
-            return
-        n_dec, E = ctx.n_decode, ctx.n_entries
-        if n_dec > 0:
-            max_len = max(ctx.h_kvlen[:n_dec])
-            if self.window is not None:
-                max_len = min(max_len, self.window + self.FAST_PAGE)
-            max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
-            base = n_dec * self.nkv * ((G + 15) // 16)
-            n_splits = self.decode_splits(base, max_pages, ops.attention_decode_resident_blocks(self.hd))
-            rows = n_dec * self.nh * n_splits
-            ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
-                                 self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
-                                 ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
-                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map)
-        if E > n_dec:
-            # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128) and the cache
-            # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.
-            tc5 = (self.prefill_kernel != "mma" and cache.tma_map is not None
-                   and ops.prefill_tc5_ok(self.hd, G, cache.page_size, cache.tma_map))
-            tpt = max(1, (ops.prefill_tc5_rows(self.hd) if tc5 else 64) // G)
-            n_tiles = ctx.prompt_tiles(tpt)
-            if tc5:
-                ops.attention_prefill_tc5(qkv, out, cache.tma_map, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
-                                          n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
-                                          self.window)
-            else:
-                ops.attention_prefill(qkv, out, cache.storage, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
-                                      n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
-                                      self.window)
+    FAST_PAGE, FAST_MAX_GROUP, WAVE_FILL = 16, 64, 2.0 / 3.0
 
 
 register_part("mixer", "attention", Attention)

@@ -58,9 +58,9 @@ class Norm(Part):
     fusable_rms = False                          # True: an RMSNorm with `.weight` and `.eps` that a ResidualTail may name
 
     def add_norm(self, resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scale: float,
-                 out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """resid (f32 [T,H]) += branch_scale * branch; out = norm(resid). With `rows`, only those
-        rows are normalised into out[0:len(rows)] and resid is left alone."""
+                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, vec: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """resid (f32 [T,H]) += branch_scale * branch (+ vec, a float32 [H] vector added to every row); out = norm(resid).
+        With `rows`, only those rows are normalised into out[0:len(rows)] and resid is left alone."""
         raise NotImplementedError
 
 
@@ -119,19 +119,22 @@ class FeedForward(Part):
 class Arrangement:
     """How the parts of one layer are wired around the residual stream."""
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward, params: Dict[str, Any]):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm], ffn: Optional[FeedForward], params: Dict[str, Any]):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
         self.params = dict(params)
 
     def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
 
     def run(self, resid: torch.Tensor, pending, ctx, cache):
         """`pending` is (branch, scale) not yet added to `resid`, or None, or an `ops.NormedInput` (the add is done and
         this block's first norm prepared; only given if `accepts_normed_input`). Returns the new pending. An arrangement
         with `takes_next_norm` has one more argument, `next_norm=None`: the first norm of the block that runs next, if that
-        block accepts a normed input; it may then return an `ops.NormedInput` for it."""
+        block accepts a normed input; it may then return an `ops.NormedInput` for it. An arrangement with `takes_pre_add`
+        has the argument `pre_add=None`: a float32 [H] vector to add to the residual stream before its first norm."""
         raise NotImplementedError
+
+    takes_pre_add = False                        # True: `run` has the `pre_add` argument
 
     takes_next_norm = False                      # True: `run` has the `next_norm` argument and may use it
 
@@ -176,4 +179,4 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from . import attention, blocks, embedding, feed_forward, norms, position  # noqa: F401
+        from . import attention, blocks, embedding, feed_forward, latent_attention, moe, norms, position  # noqa: F401

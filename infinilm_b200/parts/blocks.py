@@ -23,19 +23,27 @@ class PreNormResidual(Arrangement):
     FUSE_NORM = os.environ.get("INFINILM_B200_FUSE_NORM", "1") != "0"
 
     takes_next_norm = True
+    takes_pre_add = True
 
     def accepts_normed_input(self, T):
         return self.FUSE_NORM and self.mixer_norm.fusable_rms and self.mixer.accepts_normed(T)
 
-    def run(self, resid, pending, ctx, cache, next_norm=None):
+    def run(self, resid, pending, ctx, cache, next_norm=None, pre_add=None):
         s = float(self.params.get("residual_scale", 1.0))
         T, H = resid.shape
         fuse = self.FUSE_NORM and ctx.tap is None
         if isinstance(pending, ops.NormedInput):
+            if pre_add is not None:
+                raise ValueError("a block that adds a vector first cannot take its first norm half done")
             normed = pending
         else:
             branch, bscale = pending if pending is not None else (None, 1.0)
-            normed = self.mixer_norm.add_norm(resid, branch, bscale, ctx.ws.rows("normed", T, H, ctx.dtype))
+            if pre_add is None:
+                normed = self.mixer_norm.add_norm(resid, branch, bscale, ctx.ws.rows("normed", T, H, ctx.dtype))
+            else:
+                normed = self.mixer_norm.add_norm(resid, branch, bscale, ctx.ws.rows("normed", T, H, ctx.dtype), vec=pre_add)
+        if self.ffn is None:                      # a layer without a feed-forward: the mixer's branch is the block's
+            return self.mixer.forward(normed, ctx, cache), s
         if fuse and self.ffn_norm.fusable_rms and self.mixer.fuses_tail(T) and self.ffn.accepts_normed(T):
             normed = self.mixer.forward(normed, ctx, cache, tail=ResidualTail(resid, s, self.ffn_norm))
         else:

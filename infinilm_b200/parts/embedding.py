@@ -40,8 +40,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
-    """params: vocab, hidden, scale, tied_to (full name of the embedding table or None).
-    Logits are float32 on both paths."""
+    """params: vocab, hidden, scale, tied_to (full name of the embedding table or None), name (local tensor name,
+    default "weight"). Logits are float32 on both paths."""
     graph_safe = True
 
     def __init__(self, params, prefix, dtype):
@@ -49,16 +49,92 @@ class OutputHead(Part):
         self.vocab, self.hidden = int(params["vocab"]), int(params["hidden"])
         self.linear = Linear(self.hidden, self.vocab, dtype, alpha=float(params.get("scale", 1.0)), use_tc5=True)
         self.tied_to = params.get("tied_to")
+        self.name = str(params.get("name", "weight"))
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec("weight", (self.vocab, self.hidden), fallback=self.tied_to)]
+        return [WeightSpec(self.name, (self.vocab, self.hidden), fallback=self.tied_to)]
 
     def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
-        self.linear.set(t["weight"])
+        self.linear.set(t[self.name])
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return self.linear(x, out, out_f32=True)
 
 
+class PairPositionEmbedding(Part):
+    """Token rows times a scale, plus - each optional - a row of a second table chosen by a hash of (previous token, token)
+    and a sinusoidal position vector; the sum is made in float32 and not rounded.
+
+    params: vocab, hidden, scale, name (tensor of the table); pair: None or {buckets, mul_prev, mul_cur, name} - row
+    (prev * mul_prev + token * mul_cur) mod buckets of a [buckets + 1, hidden] table, its last row for a sequence's first
+    token; sinusoid_base: None or b - entry 2i of position p is sin(p * b^(-2i/hidden)), entry 2i+1 the cosine.
+    The previous token of a portion's first token is part of the request's state: one int32 word in a state slot
+    (token + 1; the zero state means "none"), read and written on the device, so a step never needs the host to know it
+    (a token sampled in the step before may still be on the device)."""
+    graph_safe = True
+    takes_context = True
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        self.vocab, self.hidden, self.scale = int(params["vocab"]), int(params["hidden"]), float(params.get("scale", 1.0))
+        self.name = str(params.get("name", "weight"))
+        self.pair = dict(params["pair"]) if params.get("pair") else None
+        if self.pair is not None and int(self.pair["buckets"]) <= 0:
+            raise ValueError("embedding: the pair table needs at least one bucket")
+        self.base = None if params.get("sinusoid_base") is None else float(params["sinusoid_base"])
+        self.table: Optional[torch.Tensor] = None
+        self.pair_table: Optional[torch.Tensor] = None
+        self.inv_freq: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [WeightSpec(self.name, (self.vocab, self.hidden))]
+        if self.pair is not None:
+            specs.append(WeightSpec(str(self.pair.get("name", "pair")), (int(self.pair["buckets"]) + 1, self.hidden)))
+        return specs
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        self.table = t[self.name].to(self.dtype).contiguous()
+        if self.pair is not None:
+            self.pair_table = t[str(self.pair.get("name", "pair"))].to(self.dtype).contiguous()
+        if self.base is not None:
+            i = torch.arange((self.hidden + 1) // 2, dtype=torch.float64)
+            self.inv_freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.hidden).to(torch.float32).to(self.table.device)
+
+    def cache_need(self):
+        from .spec import CacheNeed
+        return CacheNeed("state", shape=(1,), dtype="int32") if self.pair is not None else None
+
+    def forward(self, token_ids: torch.Tensor, resid: torch.Tensor, ctx, cache) -> torch.Tensor:
+        p = self.pair
+        ops.embed_pair_pos(token_ids, ctx.tok_pos, ctx.tok_entry, ctx.entry_qstart, self.table, self.scale, self.pair_table,
+                           int(p["buckets"]) if p else 0, int(p["mul_prev"]) if p else 0, int(p["mul_cur"]) if p else 0,
+                           cache.storage if cache is not None else None, cache.read_slots if cache is not None else None,
+                           cache.write_slots if cache is not None and cache.writable else None, self.inv_freq, resid)
+        return resid
+
+
+class RowTable(Part):
+    """A table of residual-wide vectors kept in float32 (they are added to the float32 residual stream).
+    params: rows, hidden, name."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        self.rows, self.hidden, self.name = int(params["rows"]), int(params["hidden"]), str(params.get("name", "weight"))
+        self.table: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.name, (self.rows, self.hidden), role="vector", init=("normal", 0.5))]
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        self.table = t[self.name].to(torch.float32).contiguous()
+        self._rows = [self.table[i] for i in range(self.rows)]
+
+    def row(self, i: int) -> torch.Tensor:
+        return self._rows[i]
+
+
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "pair_position_embedding", PairPositionEmbedding)
+register_part("embedding", "row_table", RowTable)
 register_part("head", "linear_head", OutputHead)

@@ -1,0 +1,101 @@
+"""Attention whose keys and values are up-projections of one small latent vector per token, the only thing it caches.
+
+Per token (h its normed input, H heads, d query/key dimensions and e value dimensions a head, r the latent's width):
+    c_q = rms(W_dq h) * n_q,  q = W_uq c_q                       queries through a latent of their own
+    c   = rms(W_dkv h) * n_kv                                    the cached latent
+    k_j = W_uk[j] c,  v_j = W_uv[j] c                            per head j
+    p   = softmax over the keys i <= t of (q_j . k_j) * scale, with exp(sink_j) in the denominator besides
+    y   = W_o (concat_j(sum_i p_i v_j,i) * sigmoid(W_g h))
+
+The cache holds c alone, so the products with W_uk and W_uv are moved to the query side, which changes no value:
+    q_j . (W_uk[j] c) = (W_uk[j]^T q_j) . c                      a query of width r against the latents themselves
+    sum_i p_i W_uv[j] c_i = W_uv[j] (sum_i p_i c_i)              the weighted latent, up-projected once per query
+What runs over the cache is then attention with one shared key/value head of width r, keys and values being the same
+vectors: the paged attention kernels of the framework, with a sink. No position enters anywhere.
+Norm statistics, scores, softmax and sink are float32; the products run in the compute dtype with float32 sums.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from .attention import PagedAttend
+from .base import Mixer, register_part
+from .linear import Linear
+from .spec import CacheNeed, WeightSpec
+
+
+class LatentAttention(Mixer):
+    """params: hidden, n_heads, qk_dim, v_dim, q_rank, kv_rank, scale, eps (of the two latent norms), sink (a learned
+    number per head in the softmax's denominator), gate (heads multiplied by sigmoid(W_g h)), window (None: all keys)."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        p = params
+        self.hidden, self.nh = int(p["hidden"]), int(p["n_heads"])
+        self.d, self.e = int(p["qk_dim"]), int(p["v_dim"])
+        self.qr, self.r = int(p["q_rank"]), int(p["kv_rank"])
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        self.has_sink, self.has_gate = bool(p.get("sink", True)), bool(p.get("gate", True))
+        self.window: Optional[int] = p.get("window")
+        if min(self.hidden, self.nh, self.d, self.e, self.qr, self.r) <= 0:
+            raise ValueError("latent attention: sizes must be positive")
+        if self.r > 256:
+            raise ValueError(f"latent attention: a latent of width {self.r} is beyond the attention kernels (256)")
+        self.n_down = self.qr + self.r + (self.nh * self.e if self.has_gate else 0)
+        self.down = Linear(self.hidden, self.n_down, dtype)          # rows: query latent | key/value latent | gate
+        self.up_q = Linear(self.qr, self.nh * self.d, dtype)
+        self.out = Linear(self.nh * self.e, self.hidden, dtype)
+        self.core = PagedAttend(dtype, self.nh, 1, self.r, self.scale, self.window,
+                                force_plain=bool(p.get("plain_kernel", False)), prefill_kernel=str(p.get("prefill_kernel", "auto")))
+
+    def weight_specs(self) -> List[WeightSpec]:
+        H, W = self.nh, self.hidden
+        specs = [WeightSpec("dq", (self.qr, W)), WeightSpec("dq.norm", (self.qr,), "vector", ("ones_normal", 0.05)),
+                 WeightSpec("uq", (H * self.d, self.qr), init=("normal", 0.08)),
+                 WeightSpec("dkv", (self.r, W)), WeightSpec("dkv.norm", (self.r,), "vector", ("ones_normal", 0.05)),
+                 WeightSpec("uk", (H * self.d, self.r), init=("normal", 0.08)), WeightSpec("uv", (H * self.e, self.r), init=("normal", 0.08)),
+                 WeightSpec("o", (W, H * self.e))]
+        if self.has_sink:
+            specs.append(WeightSpec("sink", (H,), "vector", ("normal", 1.0)))
+        if self.has_gate:
+            specs.append(WeightSpec("g", (H * self.e, W)))
+        return specs
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        H = self.nh
+        self.down.set(torch.cat([t["dq"], t["dkv"]] + ([t["g"]] if self.has_gate else []), dim=0))
+        self.up_q.set(t["uq"])
+        self.out.set(t["o"])
+        # W_uk[j]^T as [H, r, d]: the product that turns a head's query into a query against the latents
+        self.uk_t = t["uk"].to(self.dtype).view(H, self.d, self.r).transpose(1, 2).contiguous()
+        self.uv = t["uv"].to(self.dtype).view(H, self.e, self.r).contiguous()
+        vec = torch.float32 if self.dtype == torch.float32 else t["dq.norm"].dtype
+        self.nq, self.nkv = t["dq.norm"].to(vec).contiguous(), t["dkv.norm"].to(vec).contiguous()
+        self.core.sink = t["sink"].to(torch.float32).contiguous() if self.has_sink else None
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed("paged_kv", n_kv_heads=1, head_dim=self.r, window=self.window)
+
+    def forward(self, x, ctx, cache):
+        T, H = x.shape[0], self.nh
+        ws, dt = ctx.ws, self.dtype
+        proj = self.down(x, ws.rows("lat_down", T, self.n_down, dt))
+        cq = ws.rows("lat_cq", T, self.qr, dt)
+        ops.latent_norm_store(proj, 0, self.qr, self.qr, self.r, self.nq, self.nkv, self.eps, cq, None, ctx.tok_pos, ctx.tok_entry,
+                              cache.block_table, cache.storage if cache.writable else None, cache.page_size)
+        q = self.up_q(cq, ws.rows("lat_q", T, H * self.d, dt))
+        q_lat = ws.rows("lat_qlat", T, H * self.r, dt)
+        ops.gemm_grouped(q.view(T, H, self.d), self.uk_t, q_lat.view(T, H, self.r))
+        o_lat = ws.rows("lat_olat", T, H * self.r, dt)
+        self.core.run(q_lat, o_lat, ctx, cache)
+        o = ws.rows("lat_o", T, H * self.e, dt)
+        gate = proj[:, self.qr + self.r:].view(T, H, self.e) if self.has_gate else None
+        ops.gemm_grouped(o_lat.view(T, H, self.r), self.uv, o.view(T, H, self.e), gate=gate)
+        return self.out(o, ws.rows("branch", T, self.hidden, dt))
+
+
+register_part("mixer", "latent_attention", LatentAttention)

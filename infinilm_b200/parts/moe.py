@@ -1,0 +1,84 @@
+"""A routed feed-forward: every token runs `top` of `n_experts` small gated units, chosen by a router, plus - if the
+model has one - a shared unit that every token runs.
+
+    z = W_r h + b (float32);  the `top` largest z are chosen;  their weights are the softmax over the chosen z alone
+    y = sum_k weight_k * unit_{e_k}(h)  (+ shared(h)),   unit(h) = W_down (silu(W_gate h) * (W_up h))
+
+Everything stays on the device: the router kernel writes the choices, a sort kernel orders the (token, choice) slots by
+expert, two products over those ragged groups run the experts (gate and up as one product with the SiLU in its
+epilogue, then down), and a combine kernel sums a token's rows in the order of its choices. Nothing is read back, so a
+step can be replayed as a graph, and a token's result does not depend on what else is in the batch.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import ops
+from .base import FeedForward, register_part
+from .feed_forward import SwiGLU
+from .spec import WeightSpec
+
+
+class RoutedExperts(FeedForward):
+    """params: hidden, n_experts, top, expert_ff, shared_ff (None: no shared unit), router_bias."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        p = params
+        self.hidden, self.n, self.top, self.ff = int(p["hidden"]), int(p["n_experts"]), int(p["top"]), int(p["expert_ff"])
+        self.shared_ff = None if p.get("shared_ff") is None else int(p["shared_ff"])
+        self.router_bias = bool(p.get("router_bias", True))
+        if not 0 < self.top <= min(self.n, ops.MOE_MAX_TOP):
+            raise ValueError(f"routed experts: top {self.top} must be in 1..min(experts, {ops.MOE_MAX_TOP})")
+        self.shared = None if self.shared_ff is None else SwiGLU({"hidden": self.hidden, "intermediate": self.shared_ff}, prefix, dtype)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [WeightSpec("router", (self.n, self.hidden), init=("normal", 0.3))]
+        if self.router_bias:
+            specs.append(WeightSpec("router.b", (self.n,), "vector", ("normal", 0.3)))
+        for e in range(self.n):
+            specs += [WeightSpec(f"e{e}.gate", (self.ff, self.hidden), init=("normal", 0.05)),
+                      WeightSpec(f"e{e}.up", (self.ff, self.hidden), init=("normal", 0.05)),
+                      WeightSpec(f"e{e}.down", (self.hidden, self.ff), init=("normal", 0.05))]
+        if self.shared is not None:
+            specs += [WeightSpec("shared.gate", (self.shared_ff, self.hidden), init=("normal", 0.05)),
+                      WeightSpec("shared.up", (self.shared_ff, self.hidden), init=("normal", 0.05)),
+                      WeightSpec("shared.down", (self.hidden, self.shared_ff), init=("normal", 0.05))]
+        return specs
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        self.router = t["router"].to(self.dtype).contiguous()
+        self.router_b = t["router.b"].contiguous() if self.router_bias else None
+        if self.router_b is not None and self.dtype == torch.float32:
+            self.router_b = self.router_b.to(torch.float32)
+        # per expert: gate rows, then up rows (one product, SiLU(gate) * up in its epilogue); then down
+        self.w_gate_up = torch.stack([torch.cat([t[f"e{e}.gate"], t[f"e{e}.up"]], dim=0) for e in range(self.n)]).to(self.dtype).contiguous()
+        self.w_down = torch.stack([t[f"e{e}.down"] for e in range(self.n)]).to(self.dtype).contiguous()
+        if self.shared is not None:
+            self.shared.set_weights({"gate_proj.weight": t["shared.gate"], "up_proj.weight": t["shared.up"],
+                                     "down_proj.weight": t["shared.down"]})
+
+    def forward(self, x, ctx):
+        T, W, k = x.shape[0], self.hidden, self.top
+        ws, dt, n_slots = ctx.ws, self.dtype, x.shape[0] * self.top
+        idx = ws.rows("moe_idx", T, k, torch.int32)
+        wt = ws.rows("moe_wt", T, k, torch.float32)
+        ops.moe_route(x, self.router, self.router_b, idx, wt, k)
+        group_off = ws.flat("moe_group_off", self.n + 1, torch.int32)
+        pos_of_slot = ws.rows("moe_pos", T, k, torch.int32).view(-1)
+        row_of_pos = ws.rows("moe_row", T, k, torch.int32).view(-1)
+        ops.moe_sort(idx, self.n, group_off, pos_of_slot, row_of_pos)
+        act = ws.rows("moe_act", T, k * self.ff, dt).view(n_slots, self.ff)
+        ops.gemm_grouped(x, self.w_gate_up, act, group_off=group_off, a_rows=row_of_pos, n_rows=n_slots, glu=True)
+        y = ws.rows("moe_y", T, k * W, dt).view(n_slots, W)
+        ops.gemm_grouped(act, self.w_down, y, group_off=group_off, n_rows=n_slots)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        out = ws.rows("moe_out", T, W, dt)
+        ops.moe_combine(y, pos_of_slot, wt, shared, out)
+        return out
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

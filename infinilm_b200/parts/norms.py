@@ -16,28 +16,34 @@ from .spec import WeightSpec
 
 
 class RMSNorm(Norm):
-    """params: size, eps."""
+    """params: size, eps, weight_offset (default 0: y = x / rms * w; with 1 the stored weight is a deviation from one:
+    y = x / rms * (1 + w), the sum made in float32 when the weights are loaded), name (local tensor name, default "weight")."""
     fusable_rms = True
     graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
         self.size, self.eps = int(params["size"]), float(params["eps"])
+        self.offset = float(params.get("weight_offset", 0.0))
+        self.name = str(params.get("name", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec("weight", (self.size,), role="vector", init=("ones_normal", 0.01))]
+        init = ("ones_normal", 0.01) if self.offset == 0.0 else ("normal", 0.05)
+        return [WeightSpec(self.name, (self.size,), role="vector", init=init)]
 
     def set_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        w = tensors["weight"]
+        w = tensors[self.name]
         if w.dtype not in (torch.float32, torch.bfloat16):
             w = w.to(torch.float32)
-        if self.dtype == torch.float32:
+        if self.dtype == torch.float32 or self.offset != 0.0:
             w = w.to(torch.float32)
+        if self.offset != 0.0:
+            w = w + self.offset                   # in float32: 1 + w keeps every bit of a weight stored in bfloat16
         self.weight = w.contiguous()
 
-    def add_norm(self, resid, branch, branch_scale, out, rows=None):
-        ops.add_rmsnorm(resid, branch, branch_scale, self.weight, self.eps, out, rows)
+    def add_norm(self, resid, branch, branch_scale, out, rows=None, vec=None):
+        ops.add_rmsnorm(resid, branch, branch_scale, self.weight, self.eps, out, rows, vec)
         return out
 
 

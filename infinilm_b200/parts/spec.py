@@ -24,8 +24,8 @@ class LayerSpec:
     arrangement: str                            # registry key of the block, e.g. "prenorm_residual"
     mixer_norm: PartSpec
     mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    ffn_norm: Optional[PartSpec]                # None (with ffn None): the layer has no feed-forward
+    ffn: Optional[PartSpec]
     params: Dict[str, Any] = field(default_factory=dict)   # e.g. {"residual_scale": s}
 
 
@@ -34,9 +34,11 @@ class RunStep:
     """One entry of the run order. `layer` indexes `ModelSpec.layers`.
 
     `cache_from` names an earlier entry of the order whose cache this entry reads instead of
-    keeping its own (it then writes nothing)."""
+    keeping its own (it then writes nothing). `add_row`: row of the model's `pass_vectors` table that is added to the
+    residual stream right before this entry runs (a model that runs some layers several times marks each pass so)."""
     layer: int
     cache_from: Optional[int] = None
+    add_row: Optional[int] = None
 
 
 @dataclass
@@ -46,6 +48,7 @@ class ModelSpec:
     order: List[RunStep]
     final_norm: PartSpec
     head: PartSpec
+    pass_vectors: Optional[PartSpec] = None     # a table of residual-wide vectors that `RunStep.add_row` names
 
 
 @dataclass
@@ -75,7 +78,7 @@ class CacheNeed:
     head_dim: int = 0
     window: Optional[int] = None
     shape: Tuple[int, ...] = ()
-    dtype: str = "compute"                      # "compute" | "float32"
+    dtype: str = "compute"                      # "compute" | "float32" | "int32"
 
     def group_key(self) -> Tuple:
         return (self.kind, self.n_kv_heads, self.head_dim, self.window, tuple(self.shape), self.dtype)
