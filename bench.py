@@ -174,6 +174,9 @@ def timeline_step(args) -> int:
     from infinilm_b200.weights import random_tensors
     raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)
     raw["num_hidden_layers"] = args.layers or 4
+    if args.design != "default":                  # one of the pair of `--workload designs`, at the first of --design-sizes
+        raw = design_pair(args.design_sizes.split(",")[0], args.layers or 4)[0 if args.design == "nirozen" else 1]
+        raw["num_hidden_layers"] = args.layers or 4
     cfg = config_from_json(raw)
     B, P = args.batch, args.prompt_len
     eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
@@ -185,12 +188,14 @@ def timeline_step(args) -> int:
         ids = torch.randint(0, cfg.vocab_size, (P,), generator=g).tolist()
         for a in range(0, P, PROMPT_LEN):
             eng.step([StepEntry(s, ids[a:a + PROMPT_LEN], [])])
+    def tokens():                                 # a token of its own for every request and step
+        return torch.randint(0, cfg.vocab_size, (B,), generator=g).tolist()
     for _ in range(6):
-        eng.step([StepEntry(s, [5], [0]) for s in seqs])
+        eng.step([StepEntry(s, [t], [0]) for s, t in zip(seqs, tokens())])
     torch.cuda.synchronize()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         for _ in range(3):
-            eng.step([StepEntry(s, [5], [0]) for s in seqs])
+            eng.step([StepEntry(s, [t], [0]) for s, t in zip(seqs, tokens())])
         torch.cuda.synchronize()
     ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "emcpy" not in e.name and "emset" not in e.name),
                 key=lambda e: e.time_range.start)
@@ -202,7 +207,7 @@ def timeline_step(args) -> int:
         a = e.time_range.start - t0
         gap = f"{nxt.time_range.start - e.time_range.start:.1f}" if nxt is not None else ""
         print(f"| {a:.1f} | {e.time_range.end - e.time_range.start:.1f} | {gap} | {e.name[:64]} |")
-    print(f"\nstep: {last[-1].time_range.end - t0:.1f} us, {len(last)} kernels, {raw['num_hidden_layers']} layers, batch {B}, {P} tokens cached")
+    print(f"\nstep: {last[-1].time_range.end - t0:.1f} us, {len(last)} kernels, {args.layers or 4} layers, batch {B}, {P} tokens cached")
     return 0
 
 
@@ -264,6 +269,170 @@ def run_workload(args) -> int:
     return 0
 
 
+# ---- the latent-attention / routed-experts design beside the dense GQA model at equal size -----------------------------------
+def _moe(experts, top, ff, shared):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": shared}}
+
+
+def design_pair(size: str, layers: int):
+    """(Nirozen configuration, MiniCPM4 configuration of the same width, depth, heads, vocabulary and ACTIVE feed-forward
+    width: top * expert ff + shared ff). Layer sizes resemble published models of the kind: 64 experts of 1,408 with 6 chosen
+    and a shared unit of 2,816 at width 2,048; a small and a wide variant around it."""
+    W, H, d, qr, r, E, top, ff, sh, V = {"1k": (1024, 8, 64, 384, 128, 16, 2, 1024, 1024, 32000),
+                                          "2k": (2048, 16, 128, 768, 256, 64, 6, 1408, 2816, 32000),
+                                          "4k": (4096, 32, 128, 1536, 256, 64, 6, 2048, 4096, 32000)}[size]
+    mixer = {"heads": H, "dim": d, "vdim": d, "q_rank": qr, "kv_rank": r, "scale": d ** -0.5}
+    nz = {"architecture": "Nirozen", "vocab": V, "width": W, "norm": {"eps": 1e-5},
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+          "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": _moe(E, top, ff, sh)} for _ in range(layers)]}
+    dense = dict(CONFIG_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=2, head_dim=d,
+                 intermediate_size=top * ff + sh, vocab_size=V, rope_scaling=None, max_position_embeddings=32768, eos_token_id=[2])
+    return nz, dense
+
+
+class OpTimer:
+    """Brackets every kernel wrapper of `infinilm_b200.ops`, every library product of `Linear` and the library's grouped
+    product with CUDA events on the launching stream, for steps that run eagerly; `table()` gives microseconds and calls per name."""
+
+    def __init__(self):
+        self.records, self.saved = [], []
+
+    def _wrap(self, owner, name, label=None):
+        import torch
+        fn = getattr(owner, name)
+        timer = self
+
+        def timed(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **k)
+            e1.record()
+            lab = label or name
+            if lab == "linear":
+                x = a[1] if len(a) > 1 else k["x"]
+                lab = f"linear[{a[0].out_features}x{a[0].in_features}]" + ("" if x.shape[0] > 16 else " skinny")
+            elif lab == "gemm_grouped":
+                lab += " ragged" if k.get("group_off") is not None else " per-head"
+                lab += " glu" if k.get("glu") else ""
+            timer.records.append((lab, e0, e1))
+            return out
+        self.saved.append((owner, name, fn))
+        setattr(owner, name, timed)
+
+    def __enter__(self):
+        import torch.nn.functional as F
+
+        from infinilm_b200 import ops
+        from infinilm_b200.parts.linear import Linear
+        for name in ("embed", "embed_pair_pos", "add_rmsnorm", "swiglu", "rope_store", "attention_plain", "attention_decode",
+                     "attention_prefill", "attention_prefill_tc5", "gemm_skinny", "gemm_skinny_resid", "gemm_skinny_rope", "gemm_mid",
+                     "gemm_tc5", "latent_norm_store", "moe_route", "moe_sort", "moe_combine", "gather_rows", "gemm_grouped"):
+            self._wrap(ops, name)
+        self._wrap(Linear, "__call__", "linear")
+        if hasattr(F, "grouped_mm"):
+            self._wrap(F, "grouped_mm", "library grouped_mm")
+        return self
+
+    def __exit__(self, *exc):
+        for owner, name, fn in reversed(self.saved):
+            setattr(owner, name, fn)
+
+    def table(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for lab, e0, e1 in self.records:
+            t = out.setdefault(lab, [0.0, 0])
+            t[0] += e0.elapsed_time(e1) * 1e3
+            t[1] += 1
+        return {k: {"us": round(v[0], 1), "calls": v[1]} for k, v in sorted(out.items(), key=lambda kv: -kv[1][0])}
+
+
+def run_designs(args) -> int:
+    """Prefill tok/s (one prompt of 2,048 tokens) and decode tok/s (batch 8 and 64 over 2,048 cached tokens each, replayed as
+    graphs) of the Nirozen design at layer sizes of real models, random weights, bfloat16, beside the dense GQA model of
+    equal width, depth, heads and active feed-forward width; and for one eager step of each kind the time of every kernel
+    (CUDA events around each launch). Prints one JSON line per size."""
+    import torch
+
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.engine import Engine, StepEntry
+    from infinilm_b200.weights import random_tensors
+    hbm, tf, src = load_peaks()
+    L = args.layers or 4
+    P = PROMPT_LEN
+    for size in args.design_sizes.split(","):
+        rec = {"workload": "designs", "size": size, "layers": L, "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}}
+        for which, raw in zip(("nirozen", "dense_gqa"), design_pair(size, L)):
+            cfg = config_from_json(raw)
+            B = 64
+            eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
+                                      num_pages=B * (P // PAGE + 16) + 8, max_seqs=B + 2, max_batch_tokens=4096)
+            g = torch.Generator().manual_seed(1)
+            prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=g).tolist() for _ in range(B)]
+            n_weights = 0
+            for _, ws_ in eng.model.weight_specs():
+                k = 1
+                for d_ in ws_.shape:
+                    k *= d_
+                n_weights += k
+            res = {"weights_gb": round(2 * n_weights / 1e9, 3)}
+            # prefill: whole prompts, one a step; the median of the timed ones
+            ts = []
+            for i in range(args.warmup + 5):
+                s = eng.open(("w", i))
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                eng.step([StepEntry(s, prompts[i % B], [P - 1])])
+                b.record()
+                torch.cuda.synchronize()
+                eng.close(s)
+                if i >= args.warmup:
+                    ts.append(a.elapsed_time(b))
+            res["prefill_ms"] = round(statistics.median(ts), 3)
+            res["prefill_tok_s"] = round(P / statistics.median(ts) * 1e3)
+            s = eng.open("timed")
+            with OpTimer() as ot:
+                eng.step([StepEntry(s, prompts[0], [P - 1])])
+                res["prefill_kernels"] = ot.table()
+            eng.close(s)
+
+            def tokens(n):                        # a different token for every request and step: routing spreads as in a real batch
+                return torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
+            # decode
+            seqs = [eng.open(i) for i in range(B)]
+            for sq, pr in zip(seqs, prompts):
+                eng.step([StepEntry(sq, pr, [])])
+            for b_ in (8, 64):
+                for _ in range(2):                # (the first steps of a shape load kernels and let the library choose its own)
+                    eng.step([StepEntry(sq, [t], [0]) for sq, t in zip(seqs[:b_], tokens(b_))])
+                with OpTimer() as ot:
+                    eng.step([StepEntry(sq, [t], [0]) for sq, t in zip(seqs[:b_], tokens(b_))])
+                    res[f"decode_b{b_}_kernels"] = ot.table()
+            eng.enable_graphs()
+            for b_ in (8, 64):
+                for _ in range(max(args.warmup, 4)):
+                    eng.step([StepEntry(sq, [t], [0]) for sq, t in zip(seqs[:b_], tokens(b_))])
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                n = min(args.steps, 64)
+                feed = [tokens(b_) for _ in range(n)]
+                a.record()
+                for toks in feed:
+                    eng.step([StepEntry(sq, [t], [0]) for sq, t in zip(seqs[:b_], toks)])
+                b.record()
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(b) / n
+                res[f"decode_b{b_}_ms"] = round(ms, 4)
+                res[f"decode_b{b_}_tok_s"] = round(b_ / ms * 1e3)
+            eng.synchronize()
+            rec[which] = res
+            del eng, seqs
+            torch.cuda.empty_cache()
+        print(json.dumps(rec), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -280,7 +449,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
     ap.add_argument("--points", type=str, default="1,64", help="batch sizes of the extra decode points")
-    ap.add_argument("--workload", choices=["default", "long_context", "continuous"], default="default",
+    ap.add_argument("--design", choices=["default", "nirozen", "dense"], default="default",
+                    help="--timeline: the step of one of the pair of --workload designs instead of the benchmark model")
+    ap.add_argument("--design-sizes", type=str, default="1k,2k", help="--workload designs: layer sizes to run (1k, 2k, 4k)")
+    ap.add_argument("--workload", choices=["default", "long_context", "continuous", "designs"], default="default",
                     help="default: the benchmark line. long_context: 8 requests x 16,384-token prompts at 8B sizes, prompt "
                          "portions of 2,048 interleaved with the others' decoding, 512 new tokens each. continuous: 256 requests "
                          "at 0.5B sizes, prompts of 16..4096 tokens, 256 new tokens each. Both print their own JSON line.")
@@ -315,6 +487,8 @@ def main() -> int:
         return profile_step(args)
     if args.timeline:
         return timeline_step(args)
+    if args.workload == "designs":
+        return run_designs(args)
     if args.workload != "default":
         return run_workload(args)
     raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)

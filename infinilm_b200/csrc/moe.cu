@@ -1,7 +1,7 @@
 // Routing of a mixture-of-experts feed-forward, all on the device so that a step never waits for the host:
 //   route:   per token, router logits z = W_r h + b in f32, the `top` largest chosen (ties: the lower expert), their
-//            weights the softmax over the chosen logits alone; one warp a token, a fixed order of sums, so a token's
-//            routing does not depend on what else is in the batch.
+//            weights the softmax over the chosen logits alone; a fixed order of sums, so a token's routing does not
+//            depend on what else is in the batch.
 //   sort:    the (token, choice) slots ordered by expert: where each expert's rows start (`group_off`), the sorted place
 //            of every slot (`pos_of_slot`) and the token whose row stands at every place (`row_of_pos`). One block.
 //   combine: out[t] = sum over the token's choices, in the order of the choices, of weight * expert output row
@@ -10,24 +10,86 @@
 
 #define MOE_MAX_TOP 32
 
-template <typename TA>
-__global__ void __launch_bounds__(128) moe_route_kernel(const TA* x, int ldx, const TA* __restrict__ w, const void* __restrict__ bias, int b_kind,
-                                                        int* __restrict__ idx, float* __restrict__ wt, int T, int H, int E, int top) {
-    extern __shared__ float zs[];                 // [warps][E]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    il_pdl_begin();
-    if (t >= T) return;
-    float* z = zs + (size_t)warp * E;
-    const TA* row = x + (size_t)t * ldx;
-    for (int e = 0; e < E; ++e) {
-        const TA* wr = w + (size_t)e * H;
-        float s = 0.f;
-        for (int h = lane; h < H; h += 32) s = fmaf(il_to_f(row[h]), il_to_f(wr[h]), s);
-        s = il_warp_sum(s);
-        if (lane == 0) z[e] = s + (bias ? il_load_any(bias, b_kind, e) : 0.f);
+// Eight f32 values of a row from 16 bytes of bfloat16, or from two 16-byte loads of float32.
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x, v[2 * i + 1] = f.y;
     }
-    __syncwarp();
+}
+__device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+
+// A block routes TOK tokens: their rows stand in shared memory as f32; the eight warps deal the experts out among
+// themselves, a warp reading an expert's weight row once (16 bytes a lane and step) for all TOK tokens; a lane sums its
+// chunks in the order of the row and the warp adds the lanes' sums in a fixed tree, so a token's logits are the same
+// whatever TOK is and whatever else is in the batch. Then one warp per token picks the `top` largest.
+template <typename TA, int TOK>
+__global__ void __launch_bounds__(256) moe_route_kernel(const TA* x, int ldx, const TA* __restrict__ w, const void* __restrict__ bias, int b_kind,
+                                                        int* __restrict__ idx, float* __restrict__ wt, int T, int H, int E, int top, int vec) {
+    extern __shared__ __align__(16) float sm[];   // [TOK][H] rows, then [TOK][E] logits
+    float* xs = sm;
+    float* zs = sm + (size_t)TOK * H;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * TOK;
+    il_pdl_begin();
+    for (int i = threadIdx.x; i < TOK * H; i += 256) {
+        const int tk = i / H, h = i - tk * H;
+        xs[i] = t0 + tk < T ? il_to_f(x[(size_t)(t0 + tk) * ldx + h]) : 0.f;
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        const TA* wr = w + (size_t)e * H;
+        float s[TOK];
+#pragma unroll
+        for (int tk = 0; tk < TOK; ++tk) s[tk] = 0.f;
+        if (vec) {
+            // four 16-byte loads of the weight row in flight at a time: with one, a decode step's few blocks spend the
+            // kernel waiting for memory one load after the other
+            for (int h0 = lane * 8; h0 < H; h0 += 1024) {
+                float wv[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int h = h0 + u * 256;
+                    if (h < H) ld8(wr + h, wv[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int h = h0 + u * 256;
+                    if (h >= H) break;
+#pragma unroll
+                    for (int tk = 0; tk < TOK; ++tk) {
+                        const float4 a = *reinterpret_cast<const float4*>(xs + tk * H + h), b = *reinterpret_cast<const float4*>(xs + tk * H + h + 4);
+                        float acc = s[tk];
+                        acc = fmaf(a.x, wv[u][0], acc), acc = fmaf(a.y, wv[u][1], acc), acc = fmaf(a.z, wv[u][2], acc), acc = fmaf(a.w, wv[u][3], acc);
+                        acc = fmaf(b.x, wv[u][4], acc), acc = fmaf(b.y, wv[u][5], acc), acc = fmaf(b.z, wv[u][6], acc), acc = fmaf(b.w, wv[u][7], acc);
+                        s[tk] = acc;
+                    }
+                }
+            }
+        } else {
+            for (int h = lane; h < H; h += 32) {
+                const float wv = il_to_f(wr[h]);
+#pragma unroll
+                for (int tk = 0; tk < TOK; ++tk) s[tk] = fmaf(xs[tk * H + h], wv, s[tk]);
+            }
+        }
+        const float be = bias ? il_load_any(bias, b_kind, e) : 0.f;
+#pragma unroll
+        for (int tk = 0; tk < TOK; ++tk) {
+            const float v = il_warp_sum(s[tk]);
+            if (lane == 0) zs[tk * E + e] = v + be;
+        }
+    }
+    __syncthreads();
+    if (warp >= TOK || t0 + warp >= T) return;
+    const int t = t0 + warp;
+    float* z = zs + (size_t)warp * E;
     float chosen_v[MOE_MAX_TOP];
     float vmax = 0.f, den = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -95,34 +157,85 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
 template <typename TA>
 __global__ void moe_combine_kernel(const TA* y, const int* pos_of_slot, const float* wt, const TA* shared_rows, TA* __restrict__ out,
                                    int H, int top) {
+    __shared__ int sp[MOE_MAX_TOP];
+    __shared__ float sw[MOE_MAX_TOP];
     const int t = blockIdx.x;
     il_pdl_begin();
+    if (threadIdx.x < top) {                      // the token's places and weights once, not once per column
+        sp[threadIdx.x] = pos_of_slot[(size_t)t * top + threadIdx.x];
+        sw[threadIdx.x] = wt[(size_t)t * top + threadIdx.x];
+    }
+    __syncthreads();
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float v[MOE_MAX_TOP];
+#pragma unroll 8
+        for (int k = 0; k < top; ++k) v[k] = il_to_f(y[(size_t)sp[k] * H + h]);      // all of a column's loads before the sum
         float s = 0.f;
-        for (int k = 0; k < top; ++k)
-            s = fmaf(wt[(size_t)t * top + k], il_to_f(y[(size_t)pos_of_slot[(size_t)t * top + k] * H + h]), s);
+#pragma unroll 8
+        for (int k = 0; k < top; ++k) s = fmaf(sw[k], v[k], s);
         if (shared_rows) s += il_to_f(shared_rows[(size_t)t * H + h]);
         out[(size_t)t * H + h] = il_from_f<TA>(s);
     }
+}
+
+// out[p] = x[rows[p]]: the rows of the tokens in the order of the sorted slots, for a product that wants them contiguous.
+template <typename TA>
+__global__ void gather_rows_kernel(const TA* x, int ldx, const int* rows, TA* __restrict__ out, int H) {
+    const int p = blockIdx.x;
+    il_pdl_begin();
+    const TA* src = x + (size_t)rows[p] * ldx;
+    TA* dst = out + (size_t)p * H;
+    if ((H * sizeof(TA)) % 16 == 0 && (ldx * sizeof(TA)) % 16 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)out & 15)) {
+        const int n = H * sizeof(TA) / 16;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+IL_EXPORT int il_gather_rows(const void* x, int act_kind, int ldx, const int* rows, void* out, int n_rows, int H, cudaStream_t stream) {
+    if (n_rows <= 0) return IL_OK;
+    if (H <= 0) return IL_BAD_ARG;
+    if (act_kind == IL_F32)
+        IL_LAUNCH(gather_rows_kernel<float>, n_rows, 128, 0, stream, (const float*)x, ldx, rows, (float*)out, H);
+    else if (act_kind == IL_BF16)
+        IL_LAUNCH(gather_rows_kernel<__nv_bfloat16>, n_rows, 128, 0, stream, (const __nv_bfloat16*)x, ldx, rows, (__nv_bfloat16*)out, H);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+template <typename TA, int TOK>
+static int launch_route(const void* x, int ldx, const void* w, const void* bias, int b_kind, int* idx, float* wt, int T, int H, int E, int top,
+                        int vec, cudaStream_t stream) {
+    const size_t smem = ((size_t)TOK * H + (size_t)TOK * E) * sizeof(float);
+    if (smem > 200 * 1024) return IL_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<TA, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return 1000 + (int)e;
+    }
+    IL_LAUNCH((moe_route_kernel<TA, TOK>), (T + TOK - 1) / TOK, 256, smem, stream, (const TA*)x, ldx, (const TA*)w, bias, b_kind, idx, wt, T, H, E,
+              top, vec);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
 }
 
 IL_EXPORT int il_moe_route(const void* x, int act_kind, int ldx, const void* w, const void* bias, int b_kind, int* idx, float* wt, int T,
                            int H, int E, int top, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (H <= 0 || E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP) return IL_BAD_ARG;
-    const int warps = 4;
-    const size_t smem = (size_t)warps * E * sizeof(float);
-    if (smem > 48 * 1024) return IL_UNSUPPORTED;
+    const int vec = (H % 8 == 0 && !((uintptr_t)w & 15)) ? 1 : 0;
+    // few tokens (a decode step): a block a token, so that the experts' rows are read by as many SMs as there are tokens;
+    // many: four tokens a block share each read
+    const bool four = T > 128 && ((size_t)4 * (H + E) * sizeof(float)) <= 160 * 1024;
     if (act_kind == IL_F32)
-        IL_LAUNCH(moe_route_kernel<float>, (T + warps - 1) / warps, warps * 32, smem, stream, (const float*)x, ldx, (const float*)w, bias, b_kind,
-                  idx, wt, T, H, E, top);
-    else if (act_kind == IL_BF16)
-        IL_LAUNCH(moe_route_kernel<__nv_bfloat16>, (T + warps - 1) / warps, warps * 32, smem, stream, (const __nv_bfloat16*)x, ldx,
-                  (const __nv_bfloat16*)w, bias, b_kind, idx, wt, T, H, E, top);
-    else
-        return IL_BAD_ARG;
-    IL_LAUNCH_CHECK();
-    return IL_OK;
+        return four ? launch_route<float, 4>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
+                    : launch_route<float, 1>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
+    if (act_kind == IL_BF16)
+        return four ? launch_route<__nv_bfloat16, 4>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
+                    : launch_route<__nv_bfloat16, 1>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
+    return IL_BAD_ARG;
 }
 
 IL_EXPORT int il_moe_sort(const int* idx, int n_slots, int top, int E, int* group_off, int* pos_of_slot, int* row_of_pos, cudaStream_t stream) {

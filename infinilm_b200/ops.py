@@ -739,6 +739,17 @@ def moe_sort(idx: torch.Tensor, n_experts: int, group_off: torch.Tensor, pos_of_
     _check(f(_ptr(idx), T * top, top, n_experts, _ptr(group_off), _ptr(pos_of_slot), _ptr(row_of_pos), _stream()), "moe_sort")
 
 
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[p] = x[rows[p]] for the len(out) first entries of rows (int32 on the device)."""
+    _need_cuda(x, rows, out)
+    n, H = out.shape
+    if x.dtype != out.dtype or x.shape[1] != H or x.stride(1) != 1 or rows.dtype != torch.int32 or rows.numel() < n:
+        raise KernelError("gather_rows: x [*, H], out [n, H] of one dtype, rows int32 [n]")
+    _contig("out", out)
+    f = _fn("moe", "il_gather_rows", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), _ptr(rows), _ptr(out), n, H, _stream()), "gather_rows")
+
+
 def moe_combine(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, shared_rows: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out[t] = sum_k wt[t,k] * y[pos_of_slot[t*top + k]] (+ shared_rows[t]), summed in f32 in the order of k."""
     _need_cuda(y, pos_of_slot, wt, shared_rows, out)
