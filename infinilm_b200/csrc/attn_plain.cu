@@ -1,6 +1,6 @@
 // Plain attention over the paged cache: one warp per (token, query head), keys visited one by
 // one with an online softmax in f32. It takes any mix of prompt portions and single decoded
-// tokens, any head size up to 256, any number of heads and groups, and an optional window.
+// tokens, any head size up to 1024, any number of heads and groups, and an optional window.
 // It is the attention of the 32-bit path and the reference beside the fast bfloat16 kernels.
 // With `sink` (one f32 number per query head) the softmax's denominator also holds exp(sink[head]): a key without a
 // value whose score is the number itself, not multiplied by `scale`.
@@ -9,9 +9,8 @@
 // positions max(0, p - window + 1) .. p (window <= 0: all). Query head j reads kv head j / (nh / nkv).
 #include "common.cuh"
 
-#define AP_MAX_PER_LANE 8  // head_dim <= 256
-
-template <typename TA>
+// A lane holds head_dim / 32 elements of the query and of the output: 8 (head_dim <= 256) or 32 (<= 1024).
+template <typename TA, int AP_MAX_PER_LANE>
 __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA* __restrict__ out,
                                   const TA* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_entry, int page_size,
@@ -73,19 +72,19 @@ IL_EXPORT int il_attn_plain(const void* qkv, int act_kind, int row_stride, void*
                             const float* sink, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0) return IL_BAD_ARG;
-    if (hd > 32 * AP_MAX_PER_LANE) return IL_UNSUPPORTED;
+    if (hd > 1024) return IL_UNSUPPORTED;
     const int warps = 4;
     dim3 grid(T, (nh + warps - 1) / warps);
-    if (act_kind == IL_F32)
-        attn_plain_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)qkv, row_stride, (float*)out, (const float*)cache,
-                                                                  block_table, bt_stride, tok_pos, tok_entry, page_size, nh, nkv,
-                                                                  hd, scale, window, sink);
-    else if (act_kind == IL_BF16)
-        attn_plain_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out,
-                                                                          (const __nv_bfloat16*)cache, block_table, bt_stride, tok_pos,
-                                                                          tok_entry, page_size, nh, nkv, hd, scale, window, sink);
-    else
+#define AP_LAUNCH(TA, N)                                                                                                                \
+    attn_plain_kernel<TA, N><<<grid, warps * 32, 0, stream>>>((const TA*)qkv, row_stride, (TA*)out, (const TA*)cache, block_table, bt_stride, \
+                                                              tok_pos, tok_entry, page_size, nh, nkv, hd, scale, window, sink)
+    if (act_kind == IL_F32) {
+        if (hd <= 256) AP_LAUNCH(float, 8); else AP_LAUNCH(float, 32);
+    } else if (act_kind == IL_BF16) {
+        if (hd <= 256) AP_LAUNCH(__nv_bfloat16, 8); else AP_LAUNCH(__nv_bfloat16, 32);
+    } else
         return IL_BAD_ARG;
+#undef AP_LAUNCH
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

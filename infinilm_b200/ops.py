@@ -207,8 +207,8 @@ def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     T = qkv.shape[0]
     if out.shape != (T, n_heads * head_dim) or out.dtype != qkv.dtype or cache.dtype != qkv.dtype:
         raise KernelError("attention_plain: out [T, heads*head_dim], same dtype as qkv and cache")
-    if head_dim > 256:
-        raise KernelError(f"attention_plain: head_dim {head_dim} > 256 is not supported")
+    if head_dim > 1024:
+        raise KernelError(f"attention_plain: head_dim {head_dim} > 1024 is not supported")
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_plain", "il_attn_plain", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,

@@ -43,8 +43,8 @@ class LatentAttention(Mixer):
         self.window: Optional[int] = p.get("window")
         if min(self.hidden, self.nh, self.d, self.e, self.qr, self.r) <= 0:
             raise ValueError("latent attention: sizes must be positive")
-        if self.r > 256:
-            raise ValueError(f"latent attention: a latent of width {self.r} is beyond the attention kernels (256)")
+        if self.r > 1024:
+            raise ValueError(f"latent attention: a latent of width {self.r} is beyond the attention kernels (1024; the fast ones end at 256)")
         self.n_down = self.qr + self.r + (self.nh * self.e if self.has_gate else 0)
         self.down = Linear(self.hidden, self.n_down, dtype)          # rows: query latent | key/value latent | gate
         self.up_q = Linear(self.qr, self.nh * self.d, dtype)

@@ -57,7 +57,14 @@ def nz_d() -> dict:
             "loop": {"start": 1, "stop": 2, "times": 4}}
 
 
-NIROZEN = {"a": nz_a, "b": nz_b, "c": nz_c, "d": nz_d}
+def nz_e() -> dict:
+    # a latent wider than any fast attention kernel takes (320: the plain kernel's wide form), one layer, no shared unit, a loop of all
+    return {"architecture": "Nirozen", "vocab": 64, "width": 72, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.5, "bigram": {"buckets": 5, "mul_prev": 3, "mul_cur": 2}},
+            "layers": [_layer(2, 8, 8, 40, 320, 0.35, _moe(3, 1, 16, None))], "loop": {"start": 0, "stop": 1, "times": 2}}
+
+
+NIROZEN = {"a": nz_a, "b": nz_b, "c": nz_c, "d": nz_d, "e": nz_e}
 
 
 def make_weights(raw: dict, seed: int, sharpen: float = 6.0) -> Dict[str, torch.Tensor]:

@@ -15,7 +15,7 @@ from nirozen_configs import NIROZEN, make_weights, token_ids
 pytestmark = pytest.mark.gpu
 
 TOL = {"float32": 4e-5, "bfloat16": 5e-2}
-LENGTHS = {"a": [1, 2, 17, 70, 130], "b": [3, 33, 100], "c": [5, 48, 90], "d": [4, 65, 300]}
+LENGTHS = {"a": [1, 2, 17, 70, 130], "b": [3, 33, 100], "c": [5, 48, 90], "d": [4, 65, 300], "e": [2, 50, 60]}
 
 
 def _engine(raw, w, dtype, num_pages=48, max_seqs=4, max_batch_tokens=512):
@@ -95,7 +95,7 @@ def _run_schedule(eng, requests, schedule):
     return {k: torch.cat(v, 0) for k, v in outs.items()}
 
 
-CASES = [("a", 0), ("b", 1), ("c", 2), ("d", 3)]
+CASES = [("a", 0), ("b", 1), ("c", 2), ("d", 3), ("e", 4)]
 DTYPES = ["float32", "bfloat16"]
 
 
