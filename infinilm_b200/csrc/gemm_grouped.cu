@@ -150,22 +150,33 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(const __nv_bfloat
             const int p = r0 + mt * 16 + (lane >> 2) + 8 * h;
             if (p >= r1) continue;
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+            for (int nt = 0; nt < 2; ++nt) {
+                float out2[2];
+                const int gn0 = n0 + warp * 16 + nt * 8 + (lane & 3) * 2;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    const int gn = n0 + warp * 16 + nt * 8 + (lane & 3) * 2 + c;
-                    if (gn >= N) continue;
+                    const int gn = gn0 + c;
                     float v = acc[mt][nt][2 * h + c];
-                    if (GLU) {
-                        const float gt = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(acc2[mt][nt][2 * h + c]));
-                        v = gt / (1.f + expf(-gt)) * up;
+                    if (gn < N) {
+                        if (GLU) {
+                            const float gt = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(acc2[mt][nt][2 * h + c]));
+                            v = gt / (1.f + expf(-gt)) * up;
+                        }
+                        if (gate) {
+                            const float gt = __bfloat162float(gate[(size_t)p * ld_gate + (size_t)g * gate_gs + gn]);
+                            v = __bfloat162float(__float2bfloat16_rn(v)) / (1.f + expf(-gt));
+                        }
                     }
-                    if (gate) {
-                        const float gt = __bfloat162float(gate[(size_t)p * ld_gate + (size_t)g * gate_gs + gn]);
-                        v = __bfloat162float(__float2bfloat16_rn(v)) / (1.f + expf(-gt));
-                    }
-                    Cg[(size_t)p * ldc + gn] = __float2bfloat16_rn(v);
+                    out2[c] = v;
                 }
+                __nv_bfloat16* dst = Cg + (size_t)p * ldc + gn0;
+                if (gn0 + 1 < N && !((uintptr_t)dst & 3)) {       // a pair of neighbouring columns in one 4-byte store
+                    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(out2[0], out2[1]);
+                } else {
+                    if (gn0 < N) dst[0] = __float2bfloat16_rn(out2[0]);
+                    if (gn0 + 1 < N) dst[1] = __float2bfloat16_rn(out2[1]);
+                }
+            }
         }
 }
 

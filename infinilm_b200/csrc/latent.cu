@@ -70,3 +70,30 @@ IL_EXPORT int il_latent_norm_store(const void* proj, int act_kind, int row_strid
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
+
+// y[t, c] *= sigmoid(g[t, c]) for rows of `n` columns (y contiguous, g with a row stride): the heads' gate where the product
+// before it was the library's and has no epilogue of ours.
+template <typename TA>
+__global__ void sigmoid_gate_kernel(TA* y, const TA* g, int ldg, int n, long long total) {
+    il_pdl_begin();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / n;
+        const int c = (int)(i - t * n);
+        const float gt = il_to_f(g[(size_t)t * ldg + c]);
+        y[i] = il_from_f<TA>(il_to_f(y[i]) / (1.f + expf(-gt)));
+    }
+}
+
+IL_EXPORT int il_sigmoid_gate(void* y, int act_kind, const void* g, int ldg, int T, int n, cudaStream_t stream) {
+    if (T <= 0 || n <= 0) return IL_OK;
+    const long long total = (long long)T * n;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    if (act_kind == IL_F32)
+        IL_LAUNCH(sigmoid_gate_kernel<float>, blocks, 256, 0, stream, (float*)y, (const float*)g, ldg, n, total);
+    else if (act_kind == IL_BF16)
+        IL_LAUNCH(sigmoid_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)g, ldg, n, total);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

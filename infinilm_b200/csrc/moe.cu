@@ -25,12 +25,12 @@ __device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
     v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
 }
 
-// A block routes TOK tokens: their rows stand in shared memory as f32; the eight warps deal the experts out among
-// themselves, a warp reading an expert's weight row once (16 bytes a lane and step) for all TOK tokens; a lane sums its
+// A block routes TOK tokens: their rows stand in shared memory as f32; the block's warps deal the experts out among
+// themselves (32 warps where a block has one token, a decode step: the kernel is then a few round trips to memory per warp), a warp reading an expert's weight row once (16 bytes a lane and step) for all TOK tokens; a lane sums its
 // chunks in the order of the row and the warp adds the lanes' sums in a fixed tree, so a token's logits are the same
 // whatever TOK is and whatever else is in the batch. Then one warp per token picks the `top` largest.
-template <typename TA, int TOK>
-__global__ void __launch_bounds__(256) moe_route_kernel(const TA* x, int ldx, const TA* __restrict__ w, const void* __restrict__ bias, int b_kind,
+template <typename TA, int TOK, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(const TA* x, int ldx, const TA* __restrict__ w, const void* __restrict__ bias, int b_kind,
                                                         int* __restrict__ idx, float* __restrict__ wt, int T, int H, int E, int top, int vec) {
     extern __shared__ __align__(16) float sm[];   // [TOK][H] rows, then [TOK][E] logits
     float* xs = sm;
@@ -38,12 +38,16 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* x, int ldx, co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TOK;
     il_pdl_begin();
-    for (int i = threadIdx.x; i < TOK * H; i += 256) {
+    // Vector path: a lane multiplies 8 consecutive columns at a time; the row is kept as two halves, columns 8j..8j+3 of
+    // every chunk j in the first and 8j+4..8j+7 in the second, so that the lanes of a warp read consecutive 16-byte pieces
+    // of a half (8 consecutive floats a lane would put lanes 0 and 4 on the same banks).
+    for (int i = threadIdx.x; i < TOK * H; i += WARPS * 32) {
         const int tk = i / H, h = i - tk * H;
-        xs[i] = t0 + tk < T ? il_to_f(x[(size_t)(t0 + tk) * ldx + h]) : 0.f;
+        const int at = vec ? ((h >> 3) << 2) + (h & 3) + ((h >> 2) & 1) * (H >> 1) : h;
+        xs[tk * H + at] = t0 + tk < T ? il_to_f(x[(size_t)(t0 + tk) * ldx + h]) : 0.f;
     }
     __syncthreads();
-    for (int e = warp; e < E; e += 8) {
+    for (int e = warp; e < E; e += WARPS) {
         const TA* wr = w + (size_t)e * H;
         float s[TOK];
 #pragma unroll
@@ -64,7 +68,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* x, int ldx, co
                     if (h >= H) break;
 #pragma unroll
                     for (int tk = 0; tk < TOK; ++tk) {
-                        const float4 a = *reinterpret_cast<const float4*>(xs + tk * H + h), b = *reinterpret_cast<const float4*>(xs + tk * H + h + 4);
+                        const float4 a = *reinterpret_cast<const float4*>(xs + tk * H + (h >> 1)),
+                                     b = *reinterpret_cast<const float4*>(xs + tk * H + (H >> 1) + (h >> 1));
                         float acc = s[tk];
                         acc = fmaf(a.x, wv[u][0], acc), acc = fmaf(a.y, wv[u][1], acc), acc = fmaf(a.z, wv[u][2], acc), acc = fmaf(a.w, wv[u][3], acc);
                         acc = fmaf(b.x, wv[u][4], acc), acc = fmaf(b.y, wv[u][5], acc), acc = fmaf(b.z, wv[u][6], acc), acc = fmaf(b.w, wv[u][7], acc);
@@ -154,9 +159,25 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
     }
 }
 
+__device__ __forceinline__ float4 ld4c(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4c(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4c(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4c(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a), u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// One block a token; a thread sums four neighbouring columns (H a multiple of 4: `vec`), the token's rows one after the
+// other in the order of its choices, so the sum does not depend on the number of threads or on the batch.
 template <typename TA>
 __global__ void moe_combine_kernel(const TA* y, const int* pos_of_slot, const float* wt, const TA* shared_rows, TA* __restrict__ out,
-                                   int H, int top) {
+                                   int H, int top, int vec) {
     __shared__ int sp[MOE_MAX_TOP];
     __shared__ float sw[MOE_MAX_TOP];
     const int t = blockIdx.x;
@@ -166,13 +187,25 @@ __global__ void moe_combine_kernel(const TA* y, const int* pos_of_slot, const fl
         sw[threadIdx.x] = wt[(size_t)t * top + threadIdx.x];
     }
     __syncthreads();
+    if (vec) {
+        for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const float4 v = ld4c(y + (size_t)sp[k] * H + h);
+                const float w = sw[k];
+                s.x = fmaf(w, v.x, s.x), s.y = fmaf(w, v.y, s.y), s.z = fmaf(w, v.z, s.z), s.w = fmaf(w, v.w, s.w);
+            }
+            if (shared_rows) {
+                const float4 v = ld4c(shared_rows + (size_t)t * H + h);
+                s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+            }
+            st4c(out + (size_t)t * H + h, s);
+        }
+        return;
+    }
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float v[MOE_MAX_TOP];
-#pragma unroll 8
-        for (int k = 0; k < top; ++k) v[k] = il_to_f(y[(size_t)sp[k] * H + h]);      // all of a column's loads before the sum
         float s = 0.f;
-#pragma unroll 8
-        for (int k = 0; k < top; ++k) s = fmaf(sw[k], v[k], s);
+        for (int k = 0; k < top; ++k) s = fmaf(sw[k], il_to_f(y[(size_t)sp[k] * H + h]), s);
         if (shared_rows) s += il_to_f(shared_rows[(size_t)t * H + h]);
         out[(size_t)t * H + h] = il_from_f<TA>(s);
     }
@@ -206,16 +239,16 @@ IL_EXPORT int il_gather_rows(const void* x, int act_kind, int ldx, const int* ro
     return IL_OK;
 }
 
-template <typename TA, int TOK>
+template <typename TA, int TOK, int WARPS>
 static int launch_route(const void* x, int ldx, const void* w, const void* bias, int b_kind, int* idx, float* wt, int T, int H, int E, int top,
                         int vec, cudaStream_t stream) {
     const size_t smem = ((size_t)TOK * H + (size_t)TOK * E) * sizeof(float);
     if (smem > 200 * 1024) return IL_UNSUPPORTED;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<TA, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<TA, TOK, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return 1000 + (int)e;
     }
-    IL_LAUNCH((moe_route_kernel<TA, TOK>), (T + TOK - 1) / TOK, 256, smem, stream, (const TA*)x, ldx, (const TA*)w, bias, b_kind, idx, wt, T, H, E,
+    IL_LAUNCH((moe_route_kernel<TA, TOK, WARPS>), (T + TOK - 1) / TOK, WARPS * 32, smem, stream, (const TA*)x, ldx, (const TA*)w, bias, b_kind, idx, wt, T, H, E,
               top, vec);
     IL_LAUNCH_CHECK();
     return IL_OK;
@@ -230,11 +263,11 @@ IL_EXPORT int il_moe_route(const void* x, int act_kind, int ldx, const void* w, 
     // many: four tokens a block share each read
     const bool four = T > 128 && ((size_t)4 * (H + E) * sizeof(float)) <= 160 * 1024;
     if (act_kind == IL_F32)
-        return four ? launch_route<float, 4>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
-                    : launch_route<float, 1>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
+        return four ? launch_route<float, 4, 8>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
+                    : launch_route<float, 1, 32>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
     if (act_kind == IL_BF16)
-        return four ? launch_route<__nv_bfloat16, 4>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
-                    : launch_route<__nv_bfloat16, 1>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
+        return four ? launch_route<__nv_bfloat16, 4, 8>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
+                    : launch_route<__nv_bfloat16, 1, 32>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
     return IL_BAD_ARG;
 }
 
@@ -251,12 +284,13 @@ IL_EXPORT int il_moe_combine(const void* y, int act_kind, const int* pos_of_slot
                              int H, int top, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (H <= 0 || top <= 0) return IL_BAD_ARG;
-    const int threads = H >= 1024 ? 256 : 128;
+    const int vec = (H % 4 == 0 && !((uintptr_t)y & 15) && !((uintptr_t)out & 15) && !((uintptr_t)shared_rows & 15)) ? 1 : 0;
+    const int threads = vec ? (H >= 2048 ? 512 : H >= 1024 ? 256 : 128) : (H >= 1024 ? 256 : 128);
     if (act_kind == IL_F32)
-        IL_LAUNCH(moe_combine_kernel<float>, T, threads, 0, stream, (const float*)y, pos_of_slot, wt, (const float*)shared_rows, (float*)out, H, top);
+        IL_LAUNCH(moe_combine_kernel<float>, T, threads, 0, stream, (const float*)y, pos_of_slot, wt, (const float*)shared_rows, (float*)out, H, top, vec);
     else if (act_kind == IL_BF16)
         IL_LAUNCH(moe_combine_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)y, pos_of_slot, wt,
-                  (const __nv_bfloat16*)shared_rows, (__nv_bfloat16*)out, H, top);
+                  (const __nv_bfloat16*)shared_rows, (__nv_bfloat16*)out, H, top, vec);
     else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

@@ -331,8 +331,9 @@ def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
     """The TMA tensor maps (3 x 128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim]: one
     for boxes of [16 keys x 64 columns], one whose box is a whole page of a kv head, one whose box is the K or V of a page
     as tensor-core tiles (the last two all zero if the driver refuses them).
-    None when the attention kernels have no tensor-copy path for this geometry (head_dim not a multiple of 64)."""
-    if not cache.is_cuda or cache.dtype != torch.bfloat16 or cache.dim() != 5 or cache.shape[3] != 16 or cache.shape[4] % 64:
+    None when the attention kernels have no tensor-copy path for this geometry (head_dim not a multiple of 64, or beyond 256)."""
+    if (not cache.is_cuda or cache.dtype != torch.bfloat16 or cache.dim() != 5 or cache.shape[3] != 16 or cache.shape[4] % 64
+            or cache.shape[4] > 256):
         return None
     hd = cache.shape[4]
     lib = build.load("attn_decode", {"HEAD_DIM": hd})
@@ -700,6 +701,16 @@ def latent_norm_store(proj: torch.Tensor, off_a: int, n_a: int, off_b: int, n_b:
     _check(f(_ptr(proj), kind_of(proj.dtype), proj.stride(0), off_a, n_a, off_b, n_b, _ptr(w_a), _ptr(w_b), kind_of(w_b.dtype), eps,
              _ptr(out_a), _ptr(out_b), _ptr(tok_pos), _ptr(tok_entry), _ptr(block_table), block_table.shape[1], _ptr(cache), page_size,
              T, _stream()), "latent_norm_store")
+
+
+def sigmoid_gate(y: torch.Tensor, gate: torch.Tensor) -> None:
+    """y[t, :] *= sigmoid(gate[t, :]) in place; y [T, n] contiguous, gate [T, n] with any row stride, one dtype."""
+    _need_cuda(y, gate)
+    if y.dim() != 2 or tuple(gate.shape) != tuple(y.shape) or gate.dtype != y.dtype or gate.stride(1) != 1:
+        raise KernelError("sigmoid_gate: y [T, n], gate [T, n] of the same dtype with contiguous rows")
+    _contig("y", y)
+    f = _fn("latent", "il_sigmoid_gate", [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(y), kind_of(y.dtype), _ptr(gate), gate.stride(0), y.shape[0], y.shape[1], _stream()), "sigmoid_gate")
 
 
 MOE_MAX_TOP = 32

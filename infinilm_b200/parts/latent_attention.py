@@ -31,6 +31,11 @@ class LatentAttention(Mixer):
     """params: hidden, n_heads, qk_dim, v_dim, q_rank, kv_rank, scale, eps (of the two latent norms), sink (a learned
     number per head in the softmax's denominator), gate (heads multiplied by sigmoid(W_g h)), window (None: all keys)."""
     graph_safe = True
+    # From this many rows on, the bfloat16 path hands the two per-head products to the library's batched product (written
+    # straight into the [token, head, column] rows through a strided view) and applies the gate with a kernel of its own:
+    # this package's per-head kernel is built for a decode step's few rows (measured at 16 heads, 128 -> 256: 2.4 us for 8
+    # rows in a replayed step, but 34 us for 2,048 rows, 62 TFLOP/s).
+    LIBRARY_FROM_ROWS = 256
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
@@ -73,6 +78,7 @@ class LatentAttention(Mixer):
         # W_uk[j]^T as [H, r, d]: the product that turns a head's query into a query against the latents
         self.uk_t = t["uk"].to(self.dtype).view(H, self.d, self.r).transpose(1, 2).contiguous()
         self.uv = t["uv"].to(self.dtype).view(H, self.e, self.r).contiguous()
+        self._uk_t_kn, self._uv_kn = self.uk_t.transpose(1, 2), self.uv.transpose(1, 2)      # [H, K, N] views for the library's batched product
         vec = torch.float32 if self.dtype == torch.float32 else t["dq.norm"].dtype
         self.nq, self.nkv = t["dq.norm"].to(vec).contiguous(), t["dkv.norm"].to(vec).contiguous()
         self.core.sink = t["sink"].to(torch.float32).contiguous() if self.has_sink else None
@@ -88,13 +94,22 @@ class LatentAttention(Mixer):
         ops.latent_norm_store(proj, 0, self.qr, self.qr, self.r, self.nq, self.nkv, self.eps, cq, None, ctx.tok_pos, ctx.tok_entry,
                               cache.block_table, cache.storage if cache.writable else None, cache.page_size)
         q = self.up_q(cq, ws.rows("lat_q", T, H * self.d, dt))
+        library = dt == torch.bfloat16 and T >= self.LIBRARY_FROM_ROWS and not bool(self.params.get("own_products_only", False))
         q_lat = ws.rows("lat_qlat", T, H * self.r, dt)
-        ops.gemm_grouped(q.view(T, H, self.d), self.uk_t, q_lat.view(T, H, self.r))
+        if library:
+            torch.bmm(q.view(T, H, self.d).transpose(0, 1), self._uk_t_kn, out=q_lat.view(T, H, self.r).transpose(0, 1))
+        else:
+            ops.gemm_grouped(q.view(T, H, self.d), self.uk_t, q_lat.view(T, H, self.r))
         o_lat = ws.rows("lat_olat", T, H * self.r, dt)
         self.core.run(q_lat, o_lat, ctx, cache)
         o = ws.rows("lat_o", T, H * self.e, dt)
-        gate = proj[:, self.qr + self.r:].view(T, H, self.e) if self.has_gate else None
-        ops.gemm_grouped(o_lat.view(T, H, self.r), self.uv, o.view(T, H, self.e), gate=gate)
+        gate = proj[:, self.qr + self.r:] if self.has_gate else None
+        if library:
+            torch.bmm(o_lat.view(T, H, self.r).transpose(0, 1), self._uv_kn, out=o.view(T, H, self.e).transpose(0, 1))
+            if gate is not None:
+                ops.sigmoid_gate(o, gate)
+        else:
+            ops.gemm_grouped(o_lat.view(T, H, self.r), self.uv, o.view(T, H, self.e), gate=None if gate is None else gate.view(T, H, self.e))
         return self.out(o, ws.rows("branch", T, self.hidden, dt))
 
 

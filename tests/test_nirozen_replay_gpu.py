@@ -241,3 +241,19 @@ def test_greedy_generation_through_llm(cuda_device, name, seed, dtype):
                 assert t == int(torch.argmax(lg)), f"prompt of {len(prompt)}, token {i}: {t} != {int(torch.argmax(lg))}"
             ids.append(t)
     llm.close()
+
+
+def test_command_line_on_a_random_folder(cuda_device, tmp_path, capsys):
+    """The package's command line: write a folder of random weights for a configuration, then generate from it."""
+    import json
+
+    from infinilm_b200 import cli
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(NIROZEN["b"]()))
+    folder = str(tmp_path / "m")
+    assert cli.main(["--write-random-model", folder, "--config", str(cfg_path), "--seed", "3"]) == 0
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", RuntimeWarning)
+        rc = cli.main(["--model", folder, "--enable-paged-attn", "--block-size", "16", "--num-blocks", "32", "--prompt-len", "21",
+                       "--max-new-tokens", "9", "--batch-size", "2", "--ignore-eos", "--enable-graph", "--log-level", "ERROR"])
+    assert rc == 0
