@@ -257,3 +257,45 @@ def test_command_line_on_a_random_folder(cuda_device, tmp_path, capsys):
         rc = cli.main(["--model", folder, "--enable-paged-attn", "--block-size", "16", "--num-blocks", "32", "--prompt-len", "21",
                        "--max-new-tokens", "9", "--batch-size", "2", "--ignore-eos", "--enable-graph", "--log-level", "ERROR"])
     assert rc == 0
+
+
+def test_trace_replay_as_a_process(cuda_device, tmp_path):
+    """`bin/trace_run` on a folder of random weights, float32: five requests through four state slots and a pool of 192
+    tokens, a request left out of a step, portions beside single tokens, steps in which nothing is wanted."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.weights import random_tensors, write_model_folder
+    raw = NIROZEN["a"]()
+    cfg = config_from_json(raw)
+    folder = write_model_folder(cfg, 9, str(tmp_path / "m"))
+    w = random_tensors(cfg, 9, "cpu")
+    V = raw["vocab"]
+    seqs = {k: token_ids(n, V, 60 + n) for k, n in (("p", 40), ("q", 3), ("r", 1), ("s", 18), ("t", 33))}
+    steps = [
+        {"step": 0, "entries": [{"id": "p", "tokens": seqs["p"][:17], "want": [0, 16]}, {"id": "q", "tokens": seqs["q"][:2], "want": []},
+                                {"id": "r", "tokens": seqs["r"], "want": [0]}, {"id": "s", "tokens": seqs["s"][:16], "want": [15]}], "end": ["r"]},
+        {"step": 1, "entries": [{"id": "q", "tokens": seqs["q"][2:], "want": [0]}, {"id": "s", "tokens": seqs["s"][16:17], "want": [0]}], "end": ["q"]},
+        {"step": 2, "entries": [{"id": "t", "tokens": seqs["t"][:31], "want": []}, {"id": "p", "tokens": seqs["p"][17:19], "want": [1]},
+                                {"id": "s", "tokens": seqs["s"][17:], "want": [0]}], "end": ["s"]},
+        {"step": 3, "entries": [{"id": "t", "tokens": seqs["t"][31:32], "want": [0]}, {"id": "p", "tokens": seqs["p"][19:], "want": [0, 20]}], "end": ["p"]},
+        {"step": 4, "entries": [{"id": "t", "tokens": seqs["t"][32:], "want": [0]}], "end": ["t"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", str(out_dir),
+                           "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [x for i in range(5) for x in ("done", str(i))]
+    ref = {k: P.forward(raw, w, ids) for k, ids in seqs.items()}
+    want = {0: [ref["p"][0], ref["p"][16], ref["r"][0], ref["s"][15]], 1: [ref["q"][2], ref["s"][16]], 2: [ref["p"][18], ref["s"][17]],
+            3: [ref["t"][31], ref["p"][19], ref["p"][39]], 4: [ref["t"][32]]}
+    for step, rows in want.items():
+        got = torch.from_numpy(np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(-1, V)).double()
+        r = torch.stack(rows)
+        assert float(((got - r).abs() / r.abs().amax(dim=-1, keepdim=True)).max()) < TOL["float32"], f"step {step}"
