@@ -283,7 +283,7 @@ def design_pair(size: str, layers: int):
                                           "4k": (4096, 32, 128, 1536, 256, 64, 6, 2048, 4096, 32000)}[size]
     mixer = {"heads": H, "dim": d, "vdim": d, "q_rank": qr, "kv_rank": r, "scale": d ** -0.5}
     nz = {"architecture": "Nirozen", "vocab": V, "width": W, "norm": {"eps": 1e-5},
-          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 31}},
           "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": _moe(E, top, ff, sh)} for _ in range(layers)]}
     dense = dict(CONFIG_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=2, head_dim=d,
                  intermediate_size=top * ff + sh, vocab_size=V, rope_scaling=None, max_position_embeddings=32768, eos_token_id=[2])
