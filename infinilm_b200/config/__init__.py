@@ -8,4 +8,7 @@ def __getattr__(name):
     if name == "MiniCPM4Config":
         from ..models.minicpm4 import MiniCPM4Config
         return MiniCPM4Config
+    if name == "NirozenConfig":
+        from ..models.nirozen import NirozenConfig
+        return NirozenConfig
     raise AttributeError(name)
