@@ -1,4 +1,4 @@
-// Prefill attention over the paged cache on the 5th-generation tensor cores (head_dim 64 or 128, bfloat16):
+// Prefill attention over the paged cache on the 5th-generation tensor cores (head_dim 64, 128 or 256, bfloat16):
 // prompt portions of any length, each token attending causally (and inside its window) to what its request
 // has in the cache, earlier steps' keys and this step's own.
 //
@@ -19,6 +19,10 @@
 //   K and V each in a ring of two slots, K freed as soon as its scores are computed, V when its product is; page ids
 //   are read from the block table 32 at a time, ahead of their use), 1 tensor-memory allocation and issue of the
 //   score products, 2 issue of the output products, 3-6 softmax and output. 256 columns of tensor memory and 112 KB of shared memory: two blocks per SM.
+//   Head_dim 256 (a latent shared by all heads, say) is the same kernel with O in 256 columns: 512 columns of tensor memory
+//   (two score buffers and O need 384; allocations are powers of two) and 208 KB of shared memory, one block per SM. A
+//   key tile then carries twice the products of head_dim 128 under the same softmax, which is what one block's four
+//   softmax warps can keep up with.
 //   What was measured on the way (2,048 tokens, 32 heads on 2 kv heads, head_dim 128): P in tensor memory over its own
 //   scores held a score buffer until the product P.V had read it, and the softmax threads stood idle four clocks in
 //   ten waiting for the next scores; page ids read where they were needed and 2 KB copies (16 a tile) kept the producer
@@ -33,9 +37,9 @@
 #include "tcgen05.cuh"
 
 #ifndef HEAD_DIM
-#error "compile with -DHEAD_DIM=64 or 128"
+#error "compile with -DHEAD_DIM=64, 128 or 256"
 #endif
-static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tensor-memory prefill kernel takes head_dim 64 or 128");
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128 || HEAD_DIM == 256, "the tensor-memory prefill kernel takes head_dim 64, 128 or 256");
 
 constexpr int PT_HD = HEAD_DIM;
 constexpr int PT_HALVES = HEAD_DIM / 64;          // 128-byte column blocks of a row
@@ -51,11 +55,15 @@ constexpr int PT_ATOM = PT_HALVES * 1024;         // K and V tiles: 1 KB atoms (
 constexpr int PT_PAGE_BYTES = 2 * PT_ATOM;        // the next column block's 1 KB further; a page (16 keys) is two atoms of each
 constexpr int PT_K_BYTES = PT_TILE_PAGES * PT_PAGE_BYTES;   // K tile; the V tile has the same size
 constexpr int PT_THREADS = 224;
-constexpr int PT_TMEM_COLS = 256;
+constexpr int PT_TMEM_COLS = HEAD_DIM > 128 ? 512 : 256;      // 2 x 64 columns of scores + head_dim of O, as a power of two
+constexpr int PT_BLOCKS_PER_SM = HEAD_DIM > 128 ? 1 : 2;      // what tensor memory and shared memory hold
 constexpr int PT_COL_O = 2 * PT_KEYS;             // S buffers at columns 0 and 64, O behind them
 constexpr int PT_N_BARS = 1 + 2 * PT_K_STAGES + 2 * PT_V_STAGES + 2 + 2 + 1 + 1;
 // no slack for aligning the base: two blocks of head_dim 128 fill an SM's shared memory to within 2 KB; the base is checked instead
 constexpr int PT_SMEM = PT_Q_BYTES + PT_P_BYTES + (PT_K_STAGES + PT_V_STAGES) * PT_K_BYTES + PT_N_BARS * 8 + 16;
+static_assert(PT_SMEM <= 227 * 1024, "shared memory of a block");
+static_assert(PT_TMEM_COLS * PT_BLOCKS_PER_SM <= 512, "tensor memory of the blocks an SM is meant to hold");
+static_assert(HEAD_DIM <= 128 || 2 * PT_SMEM > 228 * 1024, "two blocks of 512 columns must not meet on an SM: shared memory keeps them apart");
 constexpr unsigned PT_SPIN = 1u << 22;
 constexpr float PT_RAISE = 8.f;                   // the running maximum follows a tile's only beyond this (log2 units)
 
@@ -75,7 +83,7 @@ __device__ __forceinline__ uint32_t pt_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
+__global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5_kernel(
     const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ qkv, int row_stride,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_qstart,
     const int* __restrict__ entry_kvlen, int first_entry, int n_entries, int nh, int nkv, float scale_log2, int window, int tpt,

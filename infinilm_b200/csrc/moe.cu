@@ -25,6 +25,39 @@ __device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
     v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
 }
 
+// One warp picks the `top` largest of a token's E logits in shared memory (overwritten), the lower expert winning a
+// tie, and writes the experts and the softmax over the chosen logits alone.
+__device__ __forceinline__ void moe_pick(float* z, int E, int top, int* __restrict__ idx, float* __restrict__ wt, int lane) {
+    float chosen_v[MOE_MAX_TOP];
+    float vmax = 0.f, den = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > bv || (v == bv && e < bi)) bv = v, bi = e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+        }
+        if (bi >= E) bi = 0;                      // every logit NaN: still a valid expert
+        if (k == 0) vmax = bv;
+        const float p = expf(bv - vmax);
+        den += p;
+        chosen_v[k] = p;
+        if (lane == 0) {
+            idx[k] = bi;
+            z[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0)
+        for (int k = 0; k < top; ++k) wt[k] = chosen_v[k] / den;
+}
+
 // A block routes TOK tokens: their rows stand in shared memory as f32; the block's warps deal the experts out among
 // themselves (32 warps where a block has one token, a decode step: the kernel is then a few round trips to memory per warp), a warp reading an expert's weight row once (16 bytes a lane and step) for all TOK tokens; a lane sums its
 // chunks in the order of the row and the warp adds the lanes' sums in a fixed tree, so a token's logits are the same
@@ -93,36 +126,23 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(const TA* x, int 
     }
     __syncthreads();
     if (warp >= TOK || t0 + warp >= T) return;
-    const int t = t0 + warp;
-    float* z = zs + (size_t)warp * E;
-    float chosen_v[MOE_MAX_TOP];
-    float vmax = 0.f, den = 0.f;
-    for (int k = 0; k < top; ++k) {
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
-            if (v > bv || (v == bv && e < bi)) bv = v, bi = e;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
-        }
-        if (bi >= E) bi = 0;                      // every logit NaN: still a valid expert
-        if (k == 0) vmax = bv;
-        const float p = expf(bv - vmax);
-        den += p;
-        chosen_v[k] = p;
-        if (lane == 0) {
-            idx[(size_t)t * top + k] = bi;
-            z[bi] = -INFINITY;
-        }
-        __syncwarp();
-    }
-    if (lane == 0)
-        for (int k = 0; k < top; ++k) wt[(size_t)t * top + k] = chosen_v[k] / den;
+    moe_pick(zs + (size_t)warp * E, E, top, idx + (size_t)(t0 + warp) * top, wt + (size_t)(t0 + warp) * top, lane);
+}
+
+// The choice alone, for logits that a matrix product has written already (z [T, ldz] f32, the bias still to be added):
+// a warp a token, its row of logits in shared memory.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) moe_select_kernel(const float* __restrict__ z, int ldz, const void* __restrict__ bias, int b_kind,
+                                                               int* __restrict__ idx, float* __restrict__ wt, int T, int E, int top) {
+    extern __shared__ __align__(16) float sm[];   // [WARPS][E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * WARPS + warp;
+    il_pdl_begin();
+    if (t >= T) return;
+    float* zs = sm + (size_t)warp * E;
+    for (int e = lane; e < E; e += 32) zs[e] = z[(size_t)t * ldz + e] + (bias ? il_load_any(bias, b_kind, e) : 0.f);
+    __syncwarp();
+    moe_pick(zs, E, top, idx + (size_t)t * top, wt + (size_t)t * top, lane);
 }
 
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int n_slots, int top, int E, int* __restrict__ group_off,
@@ -269,6 +289,21 @@ IL_EXPORT int il_moe_route(const void* x, int act_kind, int ldx, const void* w, 
         return four ? launch_route<__nv_bfloat16, 4, 8>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
                     : launch_route<__nv_bfloat16, 1, 32>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
     return IL_BAD_ARG;
+}
+
+IL_EXPORT int il_moe_select(const float* z, int ldz, const void* bias, int b_kind, int* idx, float* wt, int T, int E, int top, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP || ldz < E) return IL_BAD_ARG;
+    constexpr int WARPS = 8;
+    const size_t smem = (size_t)WARPS * E * sizeof(float);
+    if (smem > 200 * 1024) return IL_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return 1000 + (int)e;
+    }
+    IL_LAUNCH(moe_select_kernel<WARPS>, (T + WARPS - 1) / WARPS, WARPS * 32, smem, stream, z, ldz, bias, b_kind, idx, wt, T, E, top);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
 }
 
 IL_EXPORT int il_moe_sort(const int* idx, int n_slots, int top, int E, int* group_off, int* pos_of_slot, int* row_of_pos, cudaStream_t stream) {

@@ -4,7 +4,7 @@
 # other multiple of 16 up to 256 is compiled the first time a model asks for it.
 PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 PER_HEAD_DIM = ("attn_decode", "attn_prefill", "attn_decode_noalloc")
-TC5_HEAD_DIMS = {"attn_prefill_tc5": (64, 128)}      # kernels that exist for these head sizes only
+TC5_HEAD_DIMS = {"attn_prefill_tc5": (64, 128, 256)}      # kernels that exist for these head sizes only
 
 
 def all_variants():

@@ -381,7 +381,7 @@ def prefill_tc5_rows(head_dim: int) -> int:
 def prefill_tc5_ok(head_dim: int, group: int, page_size: int, kv_map: Optional[torch.Tensor] = None) -> bool:
     """Whether the tensor-memory prefill kernel takes this geometry and, if given, this tensor map of the cache (it
     needs the third map of `kv_tensor_map`, a page's K or V as tensor-core tiles)."""
-    if not (head_dim in (64, 128) and 0 < group <= 128 and page_size == 16):
+    if not (head_dim in (64, 128, 256) and 0 < group <= 128 and page_size == 16):
         return False
     return kv_map is None or _has_third_map(kv_map)
 
@@ -735,6 +735,24 @@ def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], id
                                     _c_int, _c_void_p])
     _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), _ptr(w), _ptr(bias), kind_of(bias.dtype) if bias is not None else 0, _ptr(idx),
              _ptr(wt), T, H, E, top, _stream()), "moe_route")
+
+
+def moe_select(z: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int) -> None:
+    """The choice of `moe_route` for logits a matrix product has written: z [T, E] float32 (+ bias [E]) -> idx, wt [T, top]."""
+    _need_cuda(z, bias, idx, wt)
+    T, E = z.shape
+    if z.dtype != torch.float32 or z.stride(1) != 1:
+        raise KernelError("moe_select: z float32 [T, E] with contiguous rows")
+    if idx.dtype != torch.int32 or wt.dtype != torch.float32 or tuple(idx.shape) != (T, top) or tuple(wt.shape) != (T, top):
+        raise KernelError("moe_select: idx int32 [T, top], wt float32 [T, top]")
+    if not 0 < top <= min(E, MOE_MAX_TOP):
+        raise KernelError(f"moe_select: top must be in 1..min(experts, {MOE_MAX_TOP})")
+    if bias is not None and bias.numel() != E:
+        raise KernelError("moe_select: bias [E]")
+    _contig("idx", idx), _contig("wt", wt)
+    f = _fn("moe", "il_moe_select", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(z), z.stride(0), _ptr(bias), kind_of(bias.dtype) if bias is not None else 0, _ptr(idx), _ptr(wt), T, E, top, _stream()),
+           "moe_select")
 
 
 def moe_sort(idx: torch.Tensor, n_experts: int, group_off: torch.Tensor, pos_of_slot: torch.Tensor, row_of_pos: torch.Tensor) -> None:

@@ -77,7 +77,7 @@ class PagedAttend:
                                  ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
                                  ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map, sink=self.sink)
         if E > n_dec:
-            # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128) and the cache
+            # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128, 256) and the cache
             # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.
             tc5 = (self.prefill_kernel != "mma" and cache.tma_map is not None
                    and ops.prefill_tc5_ok(self.hd, G, cache.page_size, cache.tma_map))

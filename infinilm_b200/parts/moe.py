@@ -24,6 +24,7 @@ import torch.nn.functional as F
 from .. import ops
 from .base import FeedForward, register_part
 from .feed_forward import SwiGLU
+from .linear import Linear
 from .spec import WeightSpec
 
 
@@ -34,6 +35,11 @@ class RoutedExperts(FeedForward):
     # 64 experts of 2,048 x 1,408, 6 chosen: gate+up for 512 tokens 197 us here against 171 us there, for 2,048 tokens 593
     # against 163 us; for 64 tokens 162 against 167 us, for 8 tokens 94 us (the library was not built for so few rows).
     LIBRARY_FROM_SLOTS = 2048
+    # From this many tokens on, the bfloat16 path takes the router's logits from a matrix product on the tensor cores
+    # (bfloat16 operands, which the row and the weights are anyway, exact products, float32 sums and float32 logits) and
+    # only chooses in a kernel of its own: the FFMA router re-reads every weight row for each four tokens (2,048 tokens x 64
+    # experts x 2,048: 86 us). Below it, and in float32, the router kernel computes the logits itself in a fixed order.
+    ROUTER_PRODUCT_FROM = 256
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
@@ -61,6 +67,10 @@ class RoutedExperts(FeedForward):
 
     def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
         self.router = t["router"].to(self.dtype).contiguous()
+        self.router_lin = None
+        if self.dtype == torch.bfloat16 and self.hidden % 8 == 0 and not bool(self.params.get("own_products_only", False)):
+            self.router_lin = Linear(self.hidden, self.n, self.dtype)
+            self.router_lin.set(self.router)
         self.router_b = t["router.b"].contiguous() if self.router_bias else None
         if self.router_b is not None and self.dtype == torch.float32:
             self.router_b = self.router_b.to(torch.float32)
@@ -80,7 +90,11 @@ class RoutedExperts(FeedForward):
         ws, dt, n_slots = ctx.ws, self.dtype, x.shape[0] * self.top
         idx = ws.rows("moe_idx", T, k, torch.int32)
         wt = ws.rows("moe_wt", T, k, torch.float32)
-        ops.moe_route(x, self.router, self.router_b, idx, wt, k)
+        if self.router_lin is not None and T >= self.ROUTER_PRODUCT_FROM:
+            z = self.router_lin(x, ws.rows("moe_logits", T, self.n, torch.float32), out_f32=True)
+            ops.moe_select(z, self.router_b, idx, wt, k)
+        else:
+            ops.moe_route(x, self.router, self.router_b, idx, wt, k)
         group_off = ws.flat("moe_group_off", self.n + 1, torch.int32)
         pos_of_slot = ws.rows("moe_pos", T, k, torch.int32).view(-1)
         row_of_pos = ws.rows("moe_row", T, k, torch.int32).view(-1)

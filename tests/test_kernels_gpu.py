@@ -337,7 +337,8 @@ def test_attention_prefill_bf16(cuda_device, nh, nkv, hd, window):
         close(out.cpu(), c["ref"], "bfloat16")
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(32, 2, 128), (3, 3, 64), (8, 2, 64), (6, 2, 128), (7, 1, 128), (40, 2, 64)])
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 2, 128), (3, 3, 64), (8, 2, 64), (6, 2, 128), (7, 1, 128), (40, 2, 64),
+                                       (16, 1, 256), (5, 1, 256), (8, 2, 256)])
 @pytest.mark.parametrize("window", [None, 21, 100])
 def test_attention_prefill_tc5(cuda_device, nh, nkv, hd, window):
     """The tcgen05 / tensor-memory prefill kernel: several entries with offsets, one whole prompt over many key tiles

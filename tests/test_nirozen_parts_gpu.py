@@ -110,6 +110,26 @@ def test_router_against_the_oracle(cuda_device, E, top, W):
     assert torch.allclose(wt.cpu().double(), wt_ref, atol=2e-6)
 
 
+@pytest.mark.parametrize("E,top,T", [(5, 2, 300), (64, 6, 41), (130, 32, 9), (9, 9, 17), (1, 1, 8)])
+def test_choice_from_given_logits(cuda_device, E, top, T):
+    """The choosing kernel alone (long portions in bfloat16 take their logits from a matrix product): rows of a wider
+    buffer, the bias added here, the order of the choices, ties, the softmax over the chosen."""
+    g = torch.Generator().manual_seed(E + T)
+    z = torch.randn(T, E + 3, generator=g)[:, :E]
+    z[T // 2] = z[T // 2].round()                                   # ties: the lower expert comes first
+    b = torch.randn(E, generator=g).bfloat16()
+    zz = (z + b.float()[None]).double()                             # the kernel adds the bias in float32
+    order = torch.argsort(zz, dim=1, descending=True, stable=True)[:, :top]
+    wt_ref = torch.softmax(torch.gather(zz, 1, order), dim=1)
+    idx = torch.empty(T, top, dtype=torch.int32, device="cuda")
+    wt = torch.empty(T, top, dtype=torch.float32, device="cuda")
+    zc = torch.zeros(T, E + 3, device="cuda")
+    zc[:, :E] = z.cuda()
+    ops.moe_select(zc[:, :E], b.cuda(), idx, wt, top)
+    assert torch.equal(idx.cpu().long(), order)
+    assert torch.allclose(wt.cpu().double(), wt_ref, atol=2e-6)
+
+
 def test_router_ties_take_the_lower_expert(cuda_device):
     x = torch.ones(3, 8, device="cuda")
     w = torch.zeros(6, 8, device="cuda")
@@ -117,6 +137,8 @@ def test_router_ties_take_the_lower_expert(cuda_device):
     idx = torch.empty(3, 3, dtype=torch.int32, device="cuda")
     wt = torch.empty(3, 3, dtype=torch.float32, device="cuda")
     ops.moe_route(x, w, None, idx, wt, 3)
+    assert idx.cpu().tolist() == [[4, 0, 1]] * 3
+    ops.moe_select(x @ w.t(), None, idx, wt, 3)
     assert idx.cpu().tolist() == [[4, 0, 1]] * 3
 
 
@@ -279,7 +301,8 @@ SINGLES = dict(starts=[0, 15, 16, 17, 399, 63], qlens=[1] * 6)
 
 @pytest.mark.parametrize("kernel,dtype,nh,hd", [("plain", "float32", 3, 40), ("plain", "float32", 9, 128), ("plain", "bfloat16", 5, 48),
                                                 ("prefill", "bfloat16", 5, 48), ("prefill", "bfloat16", 3, 64), ("prefill", "bfloat16", 7, 16),
-                                                ("tc5", "bfloat16", 3, 64), ("tc5", "bfloat16", 9, 128), ("tc5", "bfloat16", 1, 64)])
+                                                ("tc5", "bfloat16", 3, 64), ("tc5", "bfloat16", 9, 128), ("tc5", "bfloat16", 1, 64),
+                                                ("tc5", "bfloat16", 12, 256), ("tc5", "bfloat16", 2, 256)])
 @pytest.mark.parametrize("far", [None, (1, 3), (1, 16), (1, 255), (0, 0), (3, 15)])
 def test_sink_attention_over_portions(cuda_device, kernel, dtype, nh, hd, far):
     c = _sink_case(nh, hd, PORTIONS["starts"], PORTIONS["qlens"], nh * hd, far)
