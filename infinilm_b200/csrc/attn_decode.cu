@@ -17,6 +17,10 @@
 // boxes completing on the warp's own mbarriers, and ldmatrix reads the swizzled tiles; small per-lane
 // cp.async copies top out near 3 TB/s on this part, the tensor copies do not. Without a map (other
 // head sizes) the per-lane cp.async path with padded rows is used.
+//
+// Values that are the keys (use_tma 3: a cache whose V plane repeats its K plane, as the latent of a latent-attention
+// mixer does): only the K plane is copied, by a map whose box is that plane's page, and P.V reads the same tile
+// transposed. Half the bytes a page, half the shared memory a stage, so more blocks an SM.
 #include <cuda.h>
 #include <cstring>
 
@@ -32,6 +36,9 @@ constexpr int AD_SMEM = (AD_SMEM_PIPE > AD_SMEM_MERGE ? AD_SMEM_PIPE : AD_SMEM_M
 constexpr bool AD_TMA_OK = (HEAD_DIM % 64 == 0);
 constexpr int AD_BOXES = HEAD_DIM / 64;           // 64-column boxes of a K (or V) block
 constexpr int AD_TMA_STAGE_BYTES = 2 * AD_BOXES * 2048;   // K boxes then V boxes, each [16 x 64] bf16 = 2 KB
+constexpr int AD_TMA_STAGE_BYTES_K = AD_BOXES * 2048;        // a stage of K boxes alone (values that are the keys)
+constexpr int AD_SMEM_PIPE_K = AD_WARPS * AD_STAGES * AD_TMA_STAGE_BYTES_K;
+constexpr int AD_SMEM_K = (AD_SMEM_PIPE_K > AD_SMEM_MERGE ? AD_SMEM_PIPE_K : AD_SMEM_MERGE) + AD_WARPS * AD_STAGES * 8 + 1024;
 constexpr unsigned AD_SPIN_LIMIT = 1u << 26;
 
 __device__ __forceinline__ bool ad_mbar_wait(uint32_t bar, uint32_t parity) {
@@ -229,16 +236,20 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     };
     // the tensor-copy pipeline of this warp; its first page is asked for now if it is not the last page of the request
     const bool tma = AD_TMA_OK && use_tma;
-    const uint32_t tpipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_TMA_STAGE_BYTES;
-    const uint32_t tbars = (uint32_t)__cvta_generic_to_shared(smem) + AD_WARPS * AD_STAGES * AD_TMA_STAGE_BYTES + warp * AD_STAGES * 8;
+    const bool v_is_k = use_tma == 3;
+    const uint32_t tstage = v_is_k ? AD_TMA_STAGE_BYTES_K : AD_TMA_STAGE_BYTES;
+    const uint32_t tpipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * tstage;
+    // (the barriers stand behind whatever the merge of the warps will write over the pipeline's memory)
+    const uint32_t tbars = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * 8 +
+                           (v_is_k ? (AD_SMEM_PIPE_K > AD_SMEM_MERGE ? AD_SMEM_PIPE_K : AD_SMEM_MERGE) : AD_WARPS * AD_STAGES * AD_TMA_STAGE_BYTES);
     auto tma_issue = [&](int it) {
         if (it < n_my) {
             const int page = checked_page(it);
             if (lane == 0) {
-                const uint32_t st = tpipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, bar = tbars + (it % AD_STAGES) * 8;
+                const uint32_t st = tpipe + (it % AD_STAGES) * tstage, bar = tbars + (it % AD_STAGES) * 8;
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the tile was read by ldmatrix before
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(AD_TMA_STAGE_BYTES) : "memory");
-                if (use_tma == 2) {               // the whole page in one copy: copies of 2 KB keep the copy engine below the memory's rate
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(tstage) : "memory");
+                if (use_tma >= 2) {               // the whole page (3: its K plane) in one copy: copies of 2 KB keep the copy engine below the memory's rate
                     ad_tma_page(st, &kv_page_map, g, page, bar);
                 } else {
                     const int rk = ((page * 2) * nkv + g) * AD_PAGE, rv = ((page * 2 + 1) * nkv + g) * AD_PAGE;
@@ -315,7 +326,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
                 if (lane == 0) atomicExch(status, 21);
                 break;
             }
-            const uint32_t kt = pipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, vt = kt + AD_BOXES * 2048;
+            const uint32_t kt = pipe + (it % AD_STAGES) * tstage, vt = v_is_k ? kt : kt + AD_BOXES * 2048;
             float s[2][4];
 #pragma unroll
             for (int i = 0; i < 2; ++i)
@@ -481,15 +492,19 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
-                     int* status = nullptr, const float* sink = nullptr) {
+                     int* status = nullptr, const float* sink = nullptr, int v_is_k = 0) {
     static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
     int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
-    if (use_tma) {                                // a second map may follow the first: the page view (all zero: there is none)
-        const unsigned char* second = reinterpret_cast<const unsigned char*>(kv_map + 1);
-        for (size_t i = 0; i < sizeof(CUtensorMap) && use_tma == 1; ++i)
-            if (second[i]) use_tma = 2;
-    }
-    const CUtensorMap& page_map = use_tma == 2 ? kv_map[1] : no_map;
+    auto filled = [&](int i) {                    // maps behind the first are all zero where the driver did not take them
+        const unsigned char* b = reinterpret_cast<const unsigned char*>(kv_map + i);
+        for (size_t k = 0; k < sizeof(CUtensorMap); ++k)
+            if (b[k]) return true;
+        return false;
+    };
+    if (use_tma && filled(1)) use_tma = 2;        // the page view
+    if (use_tma && v_is_k && filled(3)) use_tma = 3;      // the K plane's page view: the V plane is never read
+    const CUtensorMap& page_map = use_tma == 3 ? kv_map[3] : use_tma == 2 ? kv_map[1] : no_map;
+    const int smem_bytes = use_tma == 3 ? AD_SMEM_K : AD_SMEM;
     static bool attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -500,7 +515,7 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     }
     const int G = nh / nkv, row_tiles = (G + 15) / 16;
     dim3 grid(n_splits, nkv * row_tiles, n_decode);
-    IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
+    IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, smem_bytes, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
         scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status,
         n_splits == 1 ? (__nv_bfloat16*)out : (__nv_bfloat16*)nullptr, sink);
@@ -522,40 +537,46 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
 
 // Blocks of the attention kernel that this device runs at once (blocks per SM from the occupancy calculator x SMs);
 // 0 if the query fails. The caller sizes the number of splits by it.
-IL_EXPORT int il_attn_decode_resident_blocks() {
-    static int cached[64];
+static int ad_resident_blocks(int v_is_k) {
+    static int cached[2][64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-    if (cached[dev]) return cached[dev];
+    const int k = (v_is_k && AD_TMA_OK) ? 1 : 0, smem = k ? AD_SMEM_K : AD_SMEM;
+    if (cached[k][dev]) return cached[k][dev];
     int per_sm = 0, sms = 0;
     if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel, AD_WARPS * 32, AD_SMEM) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel, AD_WARPS * 32, smem) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
-    cached[dev] = per_sm * sms;
-    return cached[dev];
+    cached[k][dev] = per_sm * sms;
+    return cached[k][dev];
 }
+IL_EXPORT int il_attn_decode_resident_blocks() { return ad_resident_blocks(0); }
+// ... where the values are the keys and only the K plane is staged (smaller stages, more blocks an SM)
+IL_EXPORT int il_attn_decode_resident_blocks_shared() { return ad_resident_blocks(1); }
 
 // Scratch the caller provides: o_part float32 [n_decode * nh * n_splits * head_dim], ml_part [n_decode * nh * n_splits * 2].
+// v_is_k != 0: the caller vouches that the cache's V plane repeats its K plane; with the fourth tensor map only K is read.
 IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                              int bt_stride, const int* entry_kvlen, int page_size, int n_decode, int nh, int nkv, int hd,
                              float scale, int window, int pages_per_split, int n_splits, float* o_part, float* ml_part,
-                             const void* kv_map, int* status, const float* sink, cudaStream_t stream) {
+                             const void* kv_map, int* status, const float* sink, int v_is_k, cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
-                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, sink);
+                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, sink, v_is_k);
 }
 
-// Writes two tensor maps (2 x 128 bytes at `out_maps`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16:
+// Writes four tensor maps (4 x 128 bytes at `out_maps`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16:
 // first the cache seen as rows of head_dim, for boxes of [16 rows x 64 columns] with the 128-byte swizzle; then a view
 // with the dimensions (64 columns, 16 slots, head_dim / 64 column blocks, kv heads, 2 * pages) whose box is one page
 // of one kv head, K and V: it lands in shared memory as the same 2 KB tiles, [K, V][column block][slot][64]. The second
-// is all zero if the driver does not take it; so is the third, for the prefill kernel (below). out_maps: 3 x 128 bytes.
+// is all zero if the driver does not take it; so are the third, for the prefill kernel, and the fourth, the K plane of a
+// page alone (below). out_maps: 4 x 128 bytes.
 // n_rows = pages * 2 * kv heads * 16. Returns 0, or IL_UNSUPPORTED.
 IL_EXPORT int il_attn_decode_kv_map(void* out_maps, const void* cache, long long n_rows, int hd, int nkv) {
     if (!AD_TMA_OK || hd != HEAD_DIM || nkv <= 0 || ((uintptr_t)cache & 15)) return IL_UNSUPPORTED;
@@ -570,7 +591,7 @@ IL_EXPORT int il_attn_decode_kv_map(void* out_maps, const void* cache, long long
             return IL_UNSUPPORTED;
         enc = (encode_fn)p;
     }
-    CUtensorMap m[3];
+    CUtensorMap m[4];
     memset(m, 0, sizeof(m));
     {
         cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_rows};
@@ -607,6 +628,19 @@ IL_EXPORT int il_attn_decode_kv_map(void* out_maps, const void* cache, long long
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r == CUDA_SUCCESS) m[2] = t;          // else: stays zero; the tensor-memory prefill kernel is then not used
+    }
+    {
+        // the second map with a box of one plane: at coordinate 2 * page the K plane of a page of one kv head alone
+        const cuuint64_t n_kvpages = (cuuint64_t)(n_rows / ((long long)nkv * AD_PAGE));
+        cuuint64_t dims[5] = {64, (cuuint64_t)AD_PAGE, (cuuint64_t)(hd / 64), (cuuint64_t)nkv, n_kvpages};
+        cuuint64_t strides[4] = {(cuuint64_t)hd * 2, 128, (cuuint64_t)AD_PAGE * hd * 2, (cuuint64_t)nkv * AD_PAGE * hd * 2};
+        cuuint32_t box[5] = {64, (cuuint32_t)AD_PAGE, (cuuint32_t)(hd / 64), 1, 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUtensorMap t;
+        CUresult r = enc(&t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS) m[3] = t;          // else: stays zero, both planes are read
     }
     memcpy(out_maps, m, sizeof(m));
     return IL_OK;

@@ -274,11 +274,13 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
                      entry_kvlen: torch.Tensor, n_decode: int, page_size: int, n_heads: int, n_kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
                      o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None,
-                     sink: Optional[torch.Tensor] = None) -> None:
+                     sink: Optional[torch.Tensor] = None, v_is_k: bool = False) -> None:
     """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each), then the merge of
     the splits (a second launch; with n_splits = 1 there is none and the attention kernel writes `out` itself). A row whose length is 0 gets zeros; a block-table entry below 0 is never followed.
     pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
     kv_map: the cache's tensor map from `kv_tensor_map` (pages then come in by TMA tensor copies).
+    v_is_k: the caller vouches that the V plane of every page repeats its K plane (a latent that is key and value at once);
+    with a tensor map only the K plane is then read, half the bytes.
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
     _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part, sink)
     _check_sink(sink, n_heads)
@@ -296,13 +298,13 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_decode", "il_attn_decode", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                               _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p,
-                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
     if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != KV_MAP_BYTES):
         raise KernelError("attention_decode: kv_map must be the host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
-             _ptr(sink), _stream()), "attention_decode")
+             _ptr(sink), 1 if v_is_k else 0, _stream()), "attention_decode")
     if n_splits > 1:
         count_launches(1)                         # the merge kernel (a single split needs none: the attention kernel finishes the rows)
 
@@ -310,12 +312,13 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
 _resident = {}
 
 
-def attention_decode_resident_blocks(head_dim: int) -> int:
-    """Blocks of the decode attention kernel that the current device runs at once at this head size (occupancy x SMs)."""
-    key = (torch.cuda.current_device(), head_dim)
+def attention_decode_resident_blocks(head_dim: int, v_is_k: bool = False) -> int:
+    """Blocks of the decode attention kernel that the current device runs at once at this head size (occupancy x SMs);
+    `v_is_k`: in the form that stages the K plane alone."""
+    key = (torch.cuda.current_device(), head_dim, bool(v_is_k))
     if key not in _resident:
         lib = build.load("attn_decode", {"HEAD_DIM": head_dim})
-        fn = lib.il_attn_decode_resident_blocks
+        fn = lib.il_attn_decode_resident_blocks_shared if v_is_k else lib.il_attn_decode_resident_blocks
         fn.argtypes, fn.restype = [], _c_int
         n = int(fn())
         if n <= 0:
@@ -324,13 +327,13 @@ def attention_decode_resident_blocks(head_dim: int) -> int:
     return _resident[key]
 
 
-KV_MAP_BYTES = 384
+KV_MAP_BYTES = 512
 
 
 def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
-    """The TMA tensor maps (3 x 128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim]: one
+    """The TMA tensor maps (4 x 128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim]: one
     for boxes of [16 keys x 64 columns], one whose box is a whole page of a kv head, one whose box is the K or V of a page
-    as tensor-core tiles (the last two all zero if the driver refuses them).
+    as tensor-core tiles, one whose box is the K plane of a page (the last three all zero if the driver refuses them).
     None when the attention kernels have no tensor-copy path for this geometry (head_dim not a multiple of 64, or beyond 256)."""
     if (not cache.is_cuda or cache.dtype != torch.bfloat16 or cache.dim() != 5 or cache.shape[3] != 16 or cache.shape[4] % 64
             or cache.shape[4] > 256):
@@ -392,7 +395,7 @@ def _has_third_map(kv_map: torch.Tensor) -> bool:
     ok = getattr(kv_map, "_il_third_map", None)
     if ok is None:
         ok = (not kv_map.is_cuda and kv_map.dtype == torch.uint8 and kv_map.numel() == KV_MAP_BYTES
-              and bool(kv_map[256:].any()))
+              and bool(kv_map[256:384].any()))
         kv_map._il_third_map = ok
     return ok
 

@@ -24,7 +24,9 @@ from .spec import CacheNeed, PartSpec, WeightSpec
 class PagedAttend:
     """Causal attention of a step's rows over the paged cache, by the kernel that fits each part of the step: what an
     attention mixer of any kind calls once its queries stand in rows and its keys and values in the cache.
-    `sink`: float32 [heads] on the device or None - a score per head that joins the softmax's denominator without a value."""
+    `sink`: float32 [heads] on the device or None - a score per head that joins the softmax's denominator without a value.
+    `shared_kv`: the mixer writes the same vector to the K and the V plane (one latent that is key and value); the decode
+    kernel then reads the K plane alone. The prompt kernels, bound by arithmetic, read both planes as they lie."""
 
     # The fast bfloat16 kernels take kernel pages of 16 keys (the cache manager lays larger pages out as runs of them)
     # and at most 64 query heads per kv head; anything else, and the whole float32 path, runs the plain kernel.
@@ -35,9 +37,9 @@ class PagedAttend:
     WAVE_FILL = 2.0 / 3.0                         # share of the blocks the device holds at once that the splits aim at
 
     def __init__(self, dtype, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None,
-                 force_plain: bool = False, prefill_kernel: str = "auto"):
+                 force_plain: bool = False, prefill_kernel: str = "auto", shared_kv: bool = False):
         self.dtype, self.nh, self.nkv, self.hd, self.scale, self.window = dtype, n_heads, n_kv_heads, head_dim, scale, window
-        self.force_plain, self.prefill_kernel = force_plain, prefill_kernel
+        self.force_plain, self.prefill_kernel, self.shared_kv = force_plain, prefill_kernel, shared_kv
         self.sink: Optional[torch.Tensor] = None
 
     def fast_ok(self, page_size: int) -> bool:
@@ -70,12 +72,14 @@ class PagedAttend:
                 max_len = min(max_len, self.window + self.FAST_PAGE)
             max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
             base = n_dec * self.nkv * ((G + 15) // 16)
-            n_splits = self.decode_splits(base, max_pages, ops.attention_decode_resident_blocks(self.hd))
+            v_is_k = self.shared_kv and cache.tma_map is not None
+            n_splits = self.decode_splits(base, max_pages, ops.attention_decode_resident_blocks(self.hd, v_is_k))
             rows = n_dec * self.nh * n_splits
             ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
                                  self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
                                  ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
-                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map, sink=self.sink)
+                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map, sink=self.sink,
+                                 v_is_k=v_is_k)
         if E > n_dec:
             # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128, 256) and the cache
             # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.

@@ -55,7 +55,8 @@ class LatentAttention(Mixer):
         self.up_q = Linear(self.qr, self.nh * self.d, dtype)
         self.out = Linear(self.nh * self.e, self.hidden, dtype)
         self.core = PagedAttend(dtype, self.nh, 1, self.r, self.scale, self.window,
-                                force_plain=bool(p.get("plain_kernel", False)), prefill_kernel=str(p.get("prefill_kernel", "auto")))
+                                force_plain=bool(p.get("plain_kernel", False)), prefill_kernel=str(p.get("prefill_kernel", "auto")),
+                                shared_kv=True)                      # the latent goes to both planes of the cache: decoding reads one
 
     def weight_specs(self) -> List[WeightSpec]:
         H, W = self.nh, self.hidden

@@ -277,11 +277,14 @@ def _run_kernel(kernel, c, nh, hd, scale, dtype, splits=1):
         pos = [s + i for s, ql in zip(c["starts"], c["qlens"]) for i in range(ql)]
         ent = [e for e, ql in enumerate(c["qlens"]) for _ in range(ql)]
         ops.attention_plain(q, out, cache, bt, i32(pos), i32(ent), 16, nh, 1, hd, scale, None, sink)
-    elif kernel == "decode":
+    elif kernel in ("decode", "decode_k"):
         rows = T * nh * splits
+        if kernel == "decode_k":                  # values that are the keys: the V plane must not even be read
+            cache[:, 1] = float("nan")
+            assert ops.kv_tensor_map(cache) is not None and bool(ops.kv_tensor_map(cache)[384:].any())
         ops.attention_decode(q, out, cache, bt, i32(c["lens"]), T, 16, nh, 1, hd, scale, None, 0, splits,
                              torch.empty(rows * hd, device="cuda"), torch.empty(rows * 2, device="cuda"),
-                             kv_map=ops.kv_tensor_map(cache), sink=sink)
+                             kv_map=ops.kv_tensor_map(cache), sink=sink, v_is_k=kernel == "decode_k")
     elif kernel == "prefill":
         tpt = max(1, 64 // nh)
         ops.attention_prefill(q, out, cache, bt, i32(qstart), i32(c["lens"]), 0, c["E"], sum((x + tpt - 1) // tpt for x in c["qlens"]),
@@ -311,7 +314,9 @@ def test_sink_attention_over_portions(cuda_device, kernel, dtype, nh, hd, far):
 
 
 @pytest.mark.parametrize("kernel,dtype,nh,hd,splits", [("plain", "float32", 3, 40, 1), ("decode", "bfloat16", 5, 48, 1), ("decode", "bfloat16", 3, 64, 4),
-                                                       ("decode", "bfloat16", 9, 128, 1), ("decode", "bfloat16", 9, 128, 7), ("decode", "bfloat16", 20, 32, 13)])
+                                                       ("decode", "bfloat16", 9, 128, 1), ("decode", "bfloat16", 9, 128, 7), ("decode", "bfloat16", 20, 32, 13),
+                                                       ("decode_k", "bfloat16", 3, 64, 4), ("decode_k", "bfloat16", 9, 128, 1), ("decode_k", "bfloat16", 9, 128, 7),
+                                                       ("decode_k", "bfloat16", 20, 256, 5), ("decode_k", "bfloat16", 33, 192, 2), ("decode", "bfloat16", 5, 256, 3)])
 @pytest.mark.parametrize("far", [None, (4, 2), (4, 16), (4, 383), (2, 15), (5, 0)])
 def test_sink_attention_of_single_tokens(cuda_device, kernel, dtype, nh, hd, splits, far):
     c = _sink_case(nh, hd, SINGLES["starts"], SINGLES["qlens"], nh + hd, far)
