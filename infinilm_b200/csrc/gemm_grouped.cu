@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(const __nv_bfloat
                                                                const __nv_bfloat16* __restrict__ W, int ldw, long long w_gs,
                                                                __nv_bfloat16* __restrict__ C, int ldc, long long c_gs,
                                                                const int* __restrict__ group_off, int n_groups, int M, int N, int K,
-                                                               const __nv_bfloat16* gate, int ld_gate, long long gate_gs) {
+                                                               const __nv_bfloat16* gate, int ld_gate, long long gate_gs, const float* row_scale) {
     using namespace ggm;
     constexpr int MT = BM / 16, NW = GLU ? 2 : 1;
     constexpr int A_BYTES = BM * ROW, W_BYTES = BN * ROW, STAGE_BYTES = A_BYTES + NW * W_BYTES;
@@ -149,6 +149,8 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(const __nv_bfloat
         for (int h = 0; h < 2; ++h) {
             const int p = r0 + mt * 16 + (lane >> 2) + 8 * h;
             if (p >= r1) continue;
+            // a factor per source row (the rstd of a norm that the rows of A have not been divided by yet)
+            const float rs = row_scale ? row_scale[a_rows ? a_rows[p] : p] : 1.f;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 float out2[2];
@@ -156,10 +158,10 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(const __nv_bfloat
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int gn = gn0 + c;
-                    float v = acc[mt][nt][2 * h + c];
+                    float v = acc[mt][nt][2 * h + c] * rs;
                     if (gn < N) {
                         if (GLU) {
-                            const float gt = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(acc2[mt][nt][2 * h + c]));
+                            const float gt = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(acc2[mt][nt][2 * h + c] * rs));
                             v = gt / (1.f + expf(-gt)) * up;
                         }
                         if (gate) {
@@ -290,7 +292,7 @@ IL_EXPORT int il_gemm_grouped_max_tiles(int M, int n_groups) { return (M + 63) /
 template <int BM, bool GLU>
 static int launch_mma(const void* A, int lda, long long a_gs, const int* a_rows, const void* W, int ldw, long long w_gs, void* C, int ldc,
                       long long c_gs, const int* group_off, int n_groups, int M, int N, int K, const void* gate, int ld_gate, long long gate_gs,
-                      cudaStream_t stream) {
+                      const float* row_scale, cudaStream_t stream) {
     constexpr int smem = ggm::smem_bytes<BM, GLU>();
     static bool attr_set[64];
     int dev = 0;
@@ -303,14 +305,14 @@ static int launch_mma(const void* A, int lda, long long a_gs, const int* a_rows,
     dim3 grid((N + ggm::BN - 1) / ggm::BN, group_off ? (M + BM - 1) / BM + n_groups : (M + BM - 1) / BM, group_off ? 1 : n_groups);
     if (grid.y > 65535 || grid.z > 65535) return IL_UNSUPPORTED;
     IL_LAUNCH((gemm_grouped_mma_kernel<BM, GLU>), grid, 128, smem, stream, (const __nv_bfloat16*)A, lda, a_gs, a_rows, (const __nv_bfloat16*)W, ldw,
-              w_gs, (__nv_bfloat16*)C, ldc, c_gs, group_off, n_groups, M, N, K, (const __nv_bfloat16*)gate, ld_gate, gate_gs);
+              w_gs, (__nv_bfloat16*)C, ldc, c_gs, group_off, n_groups, M, N, K, (const __nv_bfloat16*)gate, ld_gate, gate_gs, row_scale);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
 
 IL_EXPORT int il_gemm_grouped(const void* A, int act_kind, int lda, long long a_gs, const int* a_rows, const void* W, int ldw, long long w_gs,
                               void* C, int ldc, long long c_gs, const int* group_off, int n_groups, int M, int N, int K, int glu,
-                              const void* gate, int ld_gate, long long gate_gs, cudaStream_t stream) {
+                              const void* gate, int ld_gate, long long gate_gs, const float* row_scale, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || n_groups <= 0) return IL_OK;
     if (K <= 0 || (glu && gate)) return IL_BAD_ARG;
     if (act_kind == IL_BF16 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && a_gs % 8 == 0 && w_gs % 8 == 0 && !((uintptr_t)A & 15) &&
@@ -318,11 +320,12 @@ IL_EXPORT int il_gemm_grouped(const void* A, int act_kind, int lda, long long a_
         // rows of 16-byte chunks: the tensor-core kernel. Few rows a group (a decode step): tiles of 32 rows; else 64.
         const bool few = group_off ? M <= 32 * n_groups : M <= 32;
         if (glu)
-            return few ? launch_mma<32, true>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, stream)
-                       : launch_mma<64, true>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, stream);
-        return few ? launch_mma<32, false>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, stream)
-                   : launch_mma<64, false>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, stream);
+            return few ? launch_mma<32, true>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, row_scale, stream)
+                       : launch_mma<64, true>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, row_scale, stream);
+        return few ? launch_mma<32, false>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, row_scale, stream)
+                   : launch_mma<64, false>(A, lda, a_gs, a_rows, W, ldw, w_gs, C, ldc, c_gs, group_off, n_groups, M, N, K, gate, ld_gate, gate_gs, row_scale, stream);
     }
+    if (row_scale) return IL_UNSUPPORTED;         // a factor per row: the tensor-core kernel's epilogue only
     dim3 grid((N + 63) / 64, group_off ? il_gemm_grouped_max_tiles(M, n_groups) : (M + 63) / 64, group_off ? 1 : n_groups);
     if (grid.y > 65535 || grid.z > 65535) return IL_UNSUPPORTED;
 #define GG_LAUNCH(TA, G)                                                                                                                 \

@@ -64,20 +64,36 @@ __device__ __forceinline__ void moe_pick(float* z, int E, int top, int* __restri
 // whatever TOK is and whatever else is in the batch. Then one warp per token picks the `top` largest.
 template <typename TA, int TOK, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(const TA* x, int ldx, const TA* __restrict__ w, const void* __restrict__ bias, int b_kind,
-                                                        int* __restrict__ idx, float* __restrict__ wt, int T, int H, int E, int top, int vec) {
+                                                        int* __restrict__ idx, float* __restrict__ wt, int T, int H, int E, int top, int vec,
+                                                        const float* sumsq, int n_partial, float inv_h, float eps, float* __restrict__ rstd_out) {
     extern __shared__ __align__(16) float sm[];   // [TOK][H] rows, then [TOK][E] logits
+    __shared__ float rstd_s[TOK];
     float* xs = sm;
     float* zs = sm + (size_t)TOK * H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TOK;
     il_pdl_begin();
+    // Rows whose RMSNorm is not finished (x = residual * norm weight, `sumsq` the sums of the residual's squares per row
+    // and block of columns, left by the product before): the row is multiplied by rstd = rsqrt(sum / H + eps) here, in
+    // f32, and rstd is left in `rstd_out` for the products that read the same rows.
+    if (warp < TOK) {
+        float r = 1.f;
+        if (sumsq && t0 + warp < T) {
+            float sq = 0.f;
+            for (int k = lane; k < n_partial; k += 32) sq += sumsq[(size_t)(t0 + warp) * n_partial + k];
+            r = rsqrtf(il_warp_sum(sq) * inv_h + eps);
+            if (lane == 0 && rstd_out) rstd_out[t0 + warp] = r;
+        }
+        if (lane == 0) rstd_s[warp] = r;
+    }
+    __syncthreads();
     // Vector path: a lane multiplies 8 consecutive columns at a time; the row is kept as two halves, columns 8j..8j+3 of
     // every chunk j in the first and 8j+4..8j+7 in the second, so that the lanes of a warp read consecutive 16-byte pieces
     // of a half (8 consecutive floats a lane would put lanes 0 and 4 on the same banks).
     for (int i = threadIdx.x; i < TOK * H; i += WARPS * 32) {
         const int tk = i / H, h = i - tk * H;
         const int at = vec ? ((h >> 3) << 2) + (h & 3) + ((h >> 2) & 1) * (H >> 1) : h;
-        xs[tk * H + at] = t0 + tk < T ? il_to_f(x[(size_t)(t0 + tk) * ldx + h]) : 0.f;
+        xs[tk * H + at] = t0 + tk < T ? il_to_f(x[(size_t)(t0 + tk) * ldx + h]) * rstd_s[tk] : 0.f;
     }
     __syncthreads();
     for (int e = warp; e < E; e += WARPS) {
@@ -261,7 +277,7 @@ IL_EXPORT int il_gather_rows(const void* x, int act_kind, int ldx, const int* ro
 
 template <typename TA, int TOK, int WARPS>
 static int launch_route(const void* x, int ldx, const void* w, const void* bias, int b_kind, int* idx, float* wt, int T, int H, int E, int top,
-                        int vec, cudaStream_t stream) {
+                        int vec, const float* sumsq, int n_partial, float eps, float* rstd_out, cudaStream_t stream) {
     const size_t smem = ((size_t)TOK * H + (size_t)TOK * E) * sizeof(float);
     if (smem > 200 * 1024) return IL_UNSUPPORTED;
     if (smem > 48 * 1024) {
@@ -269,25 +285,27 @@ static int launch_route(const void* x, int ldx, const void* w, const void* bias,
         if (e != cudaSuccess) return 1000 + (int)e;
     }
     IL_LAUNCH((moe_route_kernel<TA, TOK, WARPS>), (T + TOK - 1) / TOK, WARPS * 32, smem, stream, (const TA*)x, ldx, (const TA*)w, bias, b_kind, idx, wt, T, H, E,
-              top, vec);
+              top, vec, sumsq, n_partial, 1.f / (float)H, eps, rstd_out);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
 
+// sumsq (or null): [T][n_partial] sums of squares of the rows' residual; x is then residual * norm weight, the router
+// finishes the norm itself and leaves rstd [T] in rstd_out (if given).
 IL_EXPORT int il_moe_route(const void* x, int act_kind, int ldx, const void* w, const void* bias, int b_kind, int* idx, float* wt, int T,
-                           int H, int E, int top, cudaStream_t stream) {
+                           int H, int E, int top, const float* sumsq, int n_partial, float eps, float* rstd_out, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
-    if (H <= 0 || E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP) return IL_BAD_ARG;
+    if (H <= 0 || E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP || (sumsq && n_partial <= 0)) return IL_BAD_ARG;
     const int vec = (H % 8 == 0 && !((uintptr_t)w & 15)) ? 1 : 0;
     // few tokens (a decode step): a block a token, so that the experts' rows are read by as many SMs as there are tokens;
     // many: four tokens a block share each read
     const bool four = T > 128 && ((size_t)4 * (H + E) * sizeof(float)) <= 160 * 1024;
     if (act_kind == IL_F32)
-        return four ? launch_route<float, 4, 8>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
-                    : launch_route<float, 1, 32>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
+        return four ? launch_route<float, 4, 8>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, sumsq, n_partial, eps, rstd_out, stream)
+                    : launch_route<float, 1, 32>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, sumsq, n_partial, eps, rstd_out, stream);
     if (act_kind == IL_BF16)
-        return four ? launch_route<__nv_bfloat16, 4, 8>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream)
-                    : launch_route<__nv_bfloat16, 1, 32>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, stream);
+        return four ? launch_route<__nv_bfloat16, 4, 8>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, sumsq, n_partial, eps, rstd_out, stream)
+                    : launch_route<__nv_bfloat16, 1, 32>(x, ldx, w, bias, b_kind, idx, wt, T, H, E, top, vec, sumsq, n_partial, eps, rstd_out, stream);
     return IL_BAD_ARG;
 }
 

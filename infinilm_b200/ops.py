@@ -719,10 +719,13 @@ def sigmoid_gate(y: torch.Tensor, gate: torch.Tensor) -> None:
 MOE_MAX_TOP = 32
 
 
-def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int) -> None:
+def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int,
+              norm_in: Optional["NormedInput"] = None, rstd_out: Optional[torch.Tensor] = None) -> None:
     """Per row of x [T,H]: logits = x w^T + bias in f32, the `top` largest experts into idx [T, top] (int32), the softmax
-    over the chosen logits into wt [T, top] (float32)."""
-    _need_cuda(x, w, bias, idx, wt)
+    over the chosen logits into wt [T, top] (float32).
+    norm_in: x is `norm_in.xw`, rows whose RMSNorm is not finished; the router multiplies them by rstd itself (in f32) and
+    leaves rstd [T] in `rstd_out` (float32) for the products that read the same rows."""
+    _need_cuda(x, w, bias, idx, wt, rstd_out)
     T, H = x.shape
     E = w.shape[0]
     if w.dtype != x.dtype or w.shape[1] != H or x.stride(1) != 1 or not w.is_contiguous():
@@ -734,10 +737,15 @@ def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], id
     if bias is not None and bias.numel() != E:
         raise KernelError("moe_route: bias [E]")
     _contig("idx", idx), _contig("wt", wt)
+    if rstd_out is not None and (rstd_out.dtype != torch.float32 or rstd_out.numel() < T or not rstd_out.is_contiguous()):
+        raise KernelError("moe_route: rstd_out float32 [T]")
+    if norm_in is not None and norm_in.width != H:
+        raise KernelError("moe_route: norm_in is of another width")
+    sq, n_partial, _, eps = _norm_args(norm_in, T)
     f = _fn("moe", "il_moe_route", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
-                                    _c_int, _c_void_p])
+                                    _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p])
     _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), _ptr(w), _ptr(bias), kind_of(bias.dtype) if bias is not None else 0, _ptr(idx),
-             _ptr(wt), T, H, E, top, _stream()), "moe_route")
+             _ptr(wt), T, H, E, top, sq, n_partial, eps, _ptr(rstd_out), _stream()), "moe_route")
 
 
 def moe_select(z: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int) -> None:
@@ -800,13 +808,18 @@ def moe_combine(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, sh
 
 def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, group_off: Optional[torch.Tensor] = None,
                  a_rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None, glu: bool = False,
-                 gate: Optional[torch.Tensor] = None) -> None:
+                 gate: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None) -> None:
     """Products over groups, out_g = a_g w_g^T, w [G, N, K] (glu: [G, 2N, K], gate rows then up rows, out = silu(gate) * up).
     Ragged (`group_off` int32 [G + 1] on the device): the `n_rows` rows of `out` [n_rows, N] stand sorted by group, group g
     owning places group_off[g] .. group_off[g+1] - 1; the row of `a` [*, K] at a place is a_rows[place] (or the place).
     Batched (no `group_off`): a [M, G, K] and out [M, G, N] are column ranges of shared rows; `gate` [M, G, N] multiplies
-    out by its sigmoid."""
-    _need_cuda(a, w, out, group_off, a_rows, gate)
+    out by its sigmoid.
+    row_scale (ragged, bfloat16 rows of 16-byte chunks): float32 per row of `a`; the products of a row are multiplied by
+    its factor before the epilogue (the rstd of a norm the rows have not been divided by)."""
+    _need_cuda(a, w, out, group_off, a_rows, gate, row_scale)
+    if row_scale is not None and (group_off is None or row_scale.dtype != torch.float32 or not row_scale.is_contiguous()
+                                  or row_scale.numel() < a.shape[0]):
+        raise KernelError("gemm_grouped: row_scale float32 [rows of a], with the ragged form")
     if w.dim() != 3 or not w.is_contiguous() or w.dtype != a.dtype or out.dtype != a.dtype:
         raise KernelError("gemm_grouped: w [G, N, K] contiguous, one dtype for a, w and out")
     G, K = w.shape[0], w.shape[2]
@@ -836,9 +849,9 @@ def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, group_o
             ldg, g_gs = gate.stride(0), gate.stride(1)
     f = _fn("gemm_grouped", "il_gemm_grouped", [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p, _c_int,
                                                 _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_ll,
-                                                _c_void_p])
+                                                _c_void_p, _c_void_p])
     _check(f(_ptr(a), kind_of(a.dtype), lda, a_gs, _ptr(a_rows), _ptr(w), w.stride(1), w.stride(0), _ptr(out), ldc, c_gs, _ptr(group_off),
-             G, M, N, K, int(glu), _ptr(gate), ldg, g_gs, _stream()), "gemm_grouped")
+             G, M, N, K, int(glu), _ptr(gate), ldg, g_gs, _ptr(row_scale), _stream()), "gemm_grouped")
 
 
 # ----------------------------------------------------------------------------------------------

@@ -87,7 +87,10 @@ class LatentAttention(Mixer):
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed("paged_kv", n_kv_heads=1, head_dim=self.r, window=self.window)
 
-    def forward(self, x, ctx, cache):
+    def fuses_tail(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_resid_ok(T, self.nh * self.e, self.hidden)
+
+    def forward(self, x, ctx, cache, tail=None):
         T, H = x.shape[0], self.nh
         ws, dt = ctx.ws, self.dtype
         proj = self.down(x, ws.rows("lat_down", T, self.n_down, dt))
@@ -111,6 +114,10 @@ class LatentAttention(Mixer):
                 ops.sigmoid_gate(o, gate)
         else:
             ops.gemm_grouped(o_lat.view(T, H, self.r), self.uv, o.view(T, H, self.e), gate=None if gate is None else gate.view(T, H, self.e))
+        if tail is not None:                      # the output product adds into the residual and prepares the next norm itself
+            return ops.gemm_skinny_resid(o, self.out.weight, self.out.alpha, self.out.bias, tail.resid, tail.scale, tail.norm.weight,
+                                         tail.norm.eps, ws.rows("xw_mixer", T, self.hidden, dt),
+                                         ws.rows("sumsq_mixer", T, (self.hidden + 15) // 16, torch.float32))
         return self.out(o, ws.rows("branch", T, self.hidden, dt))
 
 

@@ -85,12 +85,23 @@ class RoutedExperts(FeedForward):
             self.shared.set_weights({"gate_proj.weight": t["shared.gate"], "up_proj.weight": t["shared.up"],
                                      "down_proj.weight": t["shared.down"]})
 
+    def accepts_normed(self, T):
+        """A few rows (a decode step) whose norm the product before left unfinished: the router multiplies its copy of
+        the rows by rstd and hands rstd to the ragged gate+up product's epilogue; the shared unit takes such rows anyway."""
+        return (self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden) and self.hidden % 8 == 0
+                and T * self.top < self.LIBRARY_FROM_SLOTS and T < self.ROUTER_PRODUCT_FROM
+                and (self.shared is None or self.shared.accepts_normed(T)))
+
     def forward(self, x, ctx):
         T, W, k = x.shape[0], self.hidden, self.top
         ws, dt, n_slots = ctx.ws, self.dtype, x.shape[0] * self.top
         idx = ws.rows("moe_idx", T, k, torch.int32)
         wt = ws.rows("moe_wt", T, k, torch.float32)
-        if self.router_lin is not None and T >= self.ROUTER_PRODUCT_FROM:
+        normed_in, rstd = None, None
+        if isinstance(x, ops.NormedInput):       # x.xw = residual * norm weight; the division by the rms is still to come
+            normed_in, rstd = x, ws.flat("moe_rstd", T, torch.float32)
+            ops.moe_route(x.xw, self.router, self.router_b, idx, wt, k, norm_in=x, rstd_out=rstd)
+        elif self.router_lin is not None and T >= self.ROUTER_PRODUCT_FROM:
             z = self.router_lin(x, ws.rows("moe_logits", T, self.n, torch.float32), out_f32=True)
             ops.moe_select(z, self.router_b, idx, wt, k)
         else:
@@ -101,14 +112,15 @@ class RoutedExperts(FeedForward):
         ops.moe_sort(idx, self.n, group_off, pos_of_slot, row_of_pos)
         act = ws.rows("moe_act", T, k * self.ff, dt).view(n_slots, self.ff)
         y = ws.rows("moe_y", T, k * W, dt).view(n_slots, W)
-        if self.library_ok and n_slots >= self.LIBRARY_FROM_SLOTS:
+        if self.library_ok and n_slots >= self.LIBRARY_FROM_SLOTS and normed_in is None:
             xs = ws.rows("moe_x_sorted", T, k * W, dt).view(n_slots, W)
             ops.gather_rows(x, row_of_pos, xs)
             ends = group_off[1:]
             ops.swiglu(F.grouped_mm(xs, self._w_gate_up_t, offs=ends), act)
             y = F.grouped_mm(act, self._w_down_t, offs=ends)
         else:
-            ops.gemm_grouped(x, self.w_gate_up, act, group_off=group_off, a_rows=row_of_pos, n_rows=n_slots, glu=True)
+            ops.gemm_grouped(x if normed_in is None else x.xw, self.w_gate_up, act, group_off=group_off, a_rows=row_of_pos, n_rows=n_slots,
+                             glu=True, row_scale=rstd)
             ops.gemm_grouped(act, self.w_down, y, group_off=group_off, n_rows=n_slots)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         out = ws.rows("moe_out", T, W, dt)

@@ -218,6 +218,34 @@ def test_routed_feed_forward_part(cuda_device, dtype, name, layer):
             assert torch.allclose(alone.float(), both.float(), rtol=0, atol=1e-6 if dtype == "float32" else 2e-2 * float(both.abs().max()))
 
 
+@pytest.mark.parametrize("name,layer,T", [("a", 0, 1), ("a", 1, 8), ("b", 1, 16), ("d", 0, 5)])
+def test_routed_feed_forward_takes_rows_whose_norm_is_unfinished(cuda_device, name, layer, T):
+    """A decode step hands the feed-forward residual * norm weight and the sums of squares per 16 columns instead of
+    normed rows: the router and the ragged product finish the norm themselves. Against the oracle on the normed rows."""
+    from infinilm_b200.parts.moe import RoutedExperts
+    raw = NIROZEN[name]()
+    w = make_weights(raw, 11)
+    mlp, W, p = raw["layers"][layer]["mlp"], raw["width"], f"l{layer}.mlp"
+    part = RoutedExperts({"hidden": W, "n_experts": mlp["router"]["experts"], "top": mlp["router"]["top"], "expert_ff": mlp["expert"]["ff"],
+                          "shared_ff": mlp["shared"]["ff"] if mlp["shared"] else None}, p, torch.bfloat16)
+    part.set_weights({ws.name: w[part.full_name(ws.name)].cuda() for ws in part.weight_specs()})
+    assert part.accepts_normed(T)
+    g = torch.Generator().manual_seed(T)
+    resid, nw, eps = torch.randn(T, W, generator=g) * 3, 1.0 + torch.randn(W, generator=g) * 0.1, 1e-5
+    xw = (resid * nw).bfloat16()
+    pad = (-W) % 16
+    sumsq = torch.nn.functional.pad(resid * resid, (0, pad)).view(T, -1, 16).sum(-1)
+    ctx = _Ctx(torch.bfloat16)
+    got = part.forward(ops.NormedInput(xw.cuda(), sumsq.cuda().contiguous(), W, eps), ctx)
+    h = xw.double() * torch.rsqrt((resid.double() ** 2).mean(-1, keepdim=True) + eps)
+    margins = []
+    ref = P.moe(mlp, w, p, h, margins)
+    if margins:
+        keep = torch.tensor(margins).view(T, -1).amin(1) > 0.05
+        got, ref = got[keep.cuda()], ref[keep]
+    close(got, ref, "bfloat16", f"T={T}")
+
+
 # ---- attention with a sink, kernel by kernel ---------------------------------------------------------------------
 def _sink_case(nh, hd, starts, qlens, seed, far=None):
     """Entries with `starts[i]` cached positions and `qlens[i]` new ones over a cache whose K and V planes hold the same
