@@ -72,6 +72,15 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(const TA* x, int 
     float* zs = sm + (size_t)TOK * H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TOK;
+    if (TOK == 1) {
+        // A decode step: a handful of blocks, each a chain of round trips to memory. The router's weights do not come from
+        // the kernel before: the blocks ask for their lines (128 bytes a thread, dealt out over the grid) to be brought
+        // into L2 while that kernel still runs.
+        const char* wb = reinterpret_cast<const char*>(w);
+        const size_t bytes = (size_t)E * H * sizeof(TA);
+        for (size_t off = ((size_t)blockIdx.x * (WARPS * 32) + threadIdx.x) * 128; off < bytes; off += (size_t)gridDim.x * (WARPS * 32) * 128)
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wb + off));
+    }
     il_pdl_begin();
     // Rows whose RMSNorm is not finished (x = residual * norm weight, `sumsq` the sums of the residual's squares per row
     // and block of columns, left by the product before): the row is multiplied by rstd = rsqrt(sum / H + eps) here, in
@@ -161,12 +170,12 @@ __global__ void __launch_bounds__(WARPS * 32) moe_select_kernel(const float* __r
     moe_pick(zs, E, top, idx + (size_t)t * top, wt + (size_t)t * top, lane);
 }
 
-__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int n_slots, int top, int E, int* __restrict__ group_off,
-                                                        int* __restrict__ pos_of_slot, int* __restrict__ row_of_pos) {
-    extern __shared__ int sh[];                   // [E] counts, then [E] cursors
+// The body of the sort, by one whole block; `sh`: 2 * E ints of shared memory. (idx is not declared __restrict__: the
+// fused kernel below reads what its own warps have just written.)
+__device__ __forceinline__ void moe_sort_body(int* sh, const int* idx, int n_slots, int top, int E, int* __restrict__ group_off,
+                                              int* __restrict__ pos_of_slot, int* __restrict__ row_of_pos) {
     int* cnt = sh;
     int* cur = sh + E;
-    il_pdl_begin();
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
@@ -193,6 +202,85 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
             row_of_pos[p] = i / top;
         }
     }
+}
+
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* idx, int n_slots, int top, int E, int* __restrict__ group_off,
+                                                        int* __restrict__ pos_of_slot, int* __restrict__ row_of_pos) {
+    extern __shared__ int sh[];                   // [E] counts, then [E] cursors
+    il_pdl_begin();
+    moe_sort_body(sh, idx, n_slots, top, E, group_off, pos_of_slot, row_of_pos);
+}
+
+// ---- the router of a decode step (a few bfloat16 rows) as two short kernels --------------------------------------------
+// One block a token, as moe_route_kernel does it, is a chain of round trips to memory on a handful of SMs: sums of
+// squares, the row, then the weight rows of each of a warp's experts in turn, then the choice. Here a warp owns one
+// (token, expert) pair: it asks for its weight row before it waits for the kernel before (the weights do not come from
+// it), then reads the row's columns it needs straight from memory, so the logits are one round trip deep; a second kernel
+// of one block chooses for every token (a warp a token) and sorts the slots. Sums in a fixed order: a token's logits do
+// not depend on what else is in the batch.
+constexpr int ML_WARPS = 8, ML_CH = 8;            // a lane holds ML_CH chunks of 8 columns: 2,048 columns a pass
+__global__ void __launch_bounds__(ML_WARPS * 32) moe_logits_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w,
+                                                                   const void* __restrict__ bias, int b_kind, float* __restrict__ z, int T, int H, int E,
+                                                                   const float* sumsq, int n_partial, float inv_h, float eps, float* __restrict__ rstd_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * ML_WARPS + warp, t = blockIdx.y;
+    const __nv_bfloat16* wr = w + (size_t)(e < E ? e : 0) * H;
+    uint4 wv[ML_CH];
+#pragma unroll
+    for (int u = 0; u < ML_CH; ++u) {
+        const int h = lane * 8 + u * 256;
+        wv[u] = h < H ? *reinterpret_cast<const uint4*>(wr + h) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    il_pdl_begin();
+    float rstd = 1.f;
+    if (sumsq) {
+        float sq = 0.f;
+        for (int k = lane; k < n_partial; k += 32) sq += sumsq[(size_t)t * n_partial + k];
+        rstd = rsqrtf(il_warp_sum(sq) * inv_h + eps);
+        if (e == 0 && lane == 0 && rstd_out) rstd_out[t] = rstd;
+    }
+    if (e >= E) return;
+    const __nv_bfloat16* xr = x + (size_t)t * ldx;
+    float acc = 0.f;
+    for (int base = 0; base < H; base += 256 * ML_CH) {
+        uint4 xv[ML_CH];
+#pragma unroll
+        for (int u = 0; u < ML_CH; ++u) {
+            const int h = base + lane * 8 + u * 256;
+            if (base > 0) wv[u] = h < H ? *reinterpret_cast<const uint4*>(wr + h) : make_uint4(0u, 0u, 0u, 0u);
+            xv[u] = h < H ? *reinterpret_cast<const uint4*>(xr + h) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < ML_CH; ++u) {
+            const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&xv[u]);
+            const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 fa = __bfloat1622float2(a[i]), fb = __bfloat1622float2(b[i]);
+                acc = fmaf(fa.x, fb.x, acc);
+                acc = fmaf(fa.y, fb.y, acc);
+            }
+        }
+    }
+    acc = il_warp_sum(acc);
+    if (lane == 0) z[(size_t)t * E + e] = acc * rstd + (bias ? il_load_any(bias, b_kind, e) : 0.f);
+}
+
+// Chooses for every token (a warp a token, in turns) from logits z [T, E], then sorts the slots: one block.
+__global__ void __launch_bounds__(1024) moe_select_sort_kernel(const float* z, int* idx, float* __restrict__ wt, int T, int E, int top,
+                                                               int* __restrict__ group_off, int* __restrict__ pos_of_slot, int* __restrict__ row_of_pos) {
+    extern __shared__ __align__(16) float sm[];   // [32][E] logits of the warps' tokens, then 2 * E ints for the sort
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    il_pdl_begin();
+    float* zs = sm + (size_t)warp * E;
+    for (int t = warp; t < T; t += 32) {
+        for (int e = lane; e < E; e += 32) zs[e] = z[(size_t)t * E + e];
+        __syncwarp();
+        moe_pick(zs, E, top, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+        __syncwarp();
+    }
+    __syncthreads();                              // the choices, written to memory by this block's warps, are read below
+    moe_sort_body(reinterpret_cast<int*>(sm + (size_t)32 * E), idx, T * top, top, E, group_off, pos_of_slot, row_of_pos);
 }
 
 __device__ __forceinline__ float4 ld4c(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -320,6 +408,26 @@ IL_EXPORT int il_moe_select(const float* z, int ldz, const void* bias, int b_kin
         if (e != cudaSuccess) return 1000 + (int)e;
     }
     IL_LAUNCH(moe_select_kernel<WARPS>, (T + WARPS - 1) / WARPS, WARPS * 32, smem, stream, z, ldz, bias, b_kind, idx, wt, T, E, top);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// Router and sort of a few bfloat16 rows (a decode step): logits z [T, E] (scratch), then the choice and the sort in one
+// block. IL_UNSUPPORTED where the rows are not whole 16-byte chunks or the experts' logits do not fit a block's memory.
+IL_EXPORT int il_moe_route_sort_small(const void* x, int ldx, const void* w, const void* bias, int b_kind, float* z, int* idx, float* wt, int T, int H,
+                                      int E, int top, const float* sumsq, int n_partial, float eps, float* rstd_out, int* group_off,
+                                      int* pos_of_slot, int* row_of_pos, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (H <= 0 || E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP || (sumsq && n_partial <= 0)) return IL_BAD_ARG;
+    const size_t smem = (size_t)32 * E * sizeof(float) + (size_t)2 * E * sizeof(int);
+    if (H % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || smem > 200 * 1024 || T > 65535) return IL_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_select_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return 1000 + (int)e;
+    }
+    IL_LAUNCH(moe_logits_kernel, dim3((E + ML_WARPS - 1) / ML_WARPS, T), ML_WARPS * 32, 0, stream, (const __nv_bfloat16*)x, ldx,
+              (const __nv_bfloat16*)w, bias, b_kind, z, T, H, E, sumsq, n_partial, 1.f / (float)H, eps, rstd_out);
+    IL_LAUNCH(moe_select_sort_kernel, 1, 1024, smem, stream, (const float*)z, idx, wt, T, E, top, group_off, pos_of_slot, row_of_pos);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

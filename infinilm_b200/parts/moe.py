@@ -47,6 +47,7 @@ class RoutedExperts(FeedForward):
         self.hidden, self.n, self.top, self.ff = int(p["hidden"]), int(p["n_experts"]), int(p["top"]), int(p["expert_ff"])
         self.shared_ff = None if p.get("shared_ff") is None else int(p["shared_ff"])
         self.router_bias = bool(p.get("router_bias", True))
+        self.small_router = bool(p.get("small_router", True))        # False: a decode step's router as one block a token (tests compare the two)
         if not 0 < self.top <= min(self.n, ops.MOE_MAX_TOP):
             raise ValueError(f"routed experts: top {self.top} must be in 1..min(experts, {ops.MOE_MAX_TOP})")
         self.shared = None if self.shared_ff is None else SwiGLU({"hidden": self.hidden, "intermediate": self.shared_ff}, prefix, dtype)
@@ -98,18 +99,27 @@ class RoutedExperts(FeedForward):
         idx = ws.rows("moe_idx", T, k, torch.int32)
         wt = ws.rows("moe_wt", T, k, torch.float32)
         normed_in, rstd = None, None
+        group_off = ws.flat("moe_group_off", self.n + 1, torch.int32)
+        pos_of_slot = ws.rows("moe_pos", T, k, torch.int32).view(-1)
+        row_of_pos = ws.rows("moe_row", T, k, torch.int32).view(-1)
         if isinstance(x, ops.NormedInput):       # x.xw = residual * norm weight; the division by the rms is still to come
             normed_in, rstd = x, ws.flat("moe_rstd", T, torch.float32)
+        rows = x if normed_in is None else x.xw
+        small = dt == torch.bfloat16 and self.small_router and ops.route_sort_small_ok(T, W, self.n) and rows.stride(0) % 8 == 0
+        if small:
+            # a decode step: the logits a warp per (token, expert), then one block that chooses and sorts (two short kernels
+            # where a block a token was a chain of round trips to memory, and the sort a third launch)
+            ops.moe_route_sort_small(rows, self.router, self.router_b, ws.rows("moe_logits", T, self.n, torch.float32), idx, wt, k,
+                                     group_off, pos_of_slot, row_of_pos, norm_in=normed_in, rstd_out=rstd)
+        elif normed_in is not None:
             ops.moe_route(x.xw, self.router, self.router_b, idx, wt, k, norm_in=x, rstd_out=rstd)
         elif self.router_lin is not None and T >= self.ROUTER_PRODUCT_FROM:
             z = self.router_lin(x, ws.rows("moe_logits", T, self.n, torch.float32), out_f32=True)
             ops.moe_select(z, self.router_b, idx, wt, k)
         else:
             ops.moe_route(x, self.router, self.router_b, idx, wt, k)
-        group_off = ws.flat("moe_group_off", self.n + 1, torch.int32)
-        pos_of_slot = ws.rows("moe_pos", T, k, torch.int32).view(-1)
-        row_of_pos = ws.rows("moe_row", T, k, torch.int32).view(-1)
-        ops.moe_sort(idx, self.n, group_off, pos_of_slot, row_of_pos)
+        if not small:
+            ops.moe_sort(idx, self.n, group_off, pos_of_slot, row_of_pos)
         act = ws.rows("moe_act", T, k * self.ff, dt).view(n_slots, self.ff)
         y = ws.rows("moe_y", T, k * W, dt).view(n_slots, W)
         if self.library_ok and n_slots >= self.LIBRARY_FROM_SLOTS and normed_in is None:

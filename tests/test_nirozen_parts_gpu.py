@@ -130,6 +130,46 @@ def test_choice_from_given_logits(cuda_device, E, top, T):
     assert torch.allclose(wt.cpu().double(), wt_ref, atol=2e-6)
 
 
+@pytest.mark.parametrize("E,top,W,T", [(64, 6, 2048, 8), (5, 2, 96, 1), (7, 7, 160, 16), (130, 32, 72, 3), (16, 4, 4088, 13)])
+@pytest.mark.parametrize("unfinished", [False, True])
+def test_router_of_a_few_rows_as_two_kernels(cuda_device, E, top, W, T, unfinished):
+    """A decode step's router (logits a warp per token and expert, then one block that chooses and sorts) against the
+    oracle and against the sort kernel; also on rows whose norm is unfinished, where it leaves rstd per row."""
+    g = torch.Generator().manual_seed(E + T)
+    w = {"r.router": (torch.randn(E, W, generator=g) * 0.3).bfloat16(), "r.router.b": (torch.randn(E, generator=g)).bfloat16()}
+    resid = torch.randn(T, W, generator=g) * (2.0 if unfinished else 1.0)
+    xw = resid.bfloat16()
+    eps = 1e-5
+    rstd_ref = torch.rsqrt((resid.double() ** 2).mean(-1, keepdim=True) + eps) if unfinished else torch.ones(T, 1, dtype=torch.float64)
+    idx_ref, wt_ref, z_ref = P.route({"router": {"top": top}}, w, "r", xw.double() * rstd_ref)
+    srt = z_ref.sort(dim=1, descending=True).values
+    sure = ((srt[:, :top] - srt[:, 1:top + 1]).amin(1) > 1e-4) if top < E else ((srt[:, :-1] - srt[:, 1:]).amin(1) > 1e-4)
+    dev = dict(device="cuda")
+    idx, wt = torch.empty(T, top, dtype=torch.int32, **dev), torch.empty(T, top, dtype=torch.float32, **dev)
+    z = torch.empty(T, E, **dev)
+    group_off, pos, row = torch.empty(E + 1, dtype=torch.int32, **dev), torch.empty(T * top, dtype=torch.int32, **dev), torch.empty(T * top, dtype=torch.int32, **dev)
+    norm_in, rstd = None, None
+    if unfinished:
+        pad = (-W) % 16
+        sumsq = torch.nn.functional.pad(resid * resid, (0, pad)).view(T, -1, 16).sum(-1)
+        norm_in, rstd = ops.NormedInput(xw.cuda(), sumsq.cuda().contiguous(), W, eps), torch.empty(T, **dev)
+    assert ops.route_sort_small_ok(T, W, E)
+    ops.moe_route_sort_small(xw.cuda(), w["r.router"].cuda(), w["r.router.b"].cuda(), z, idx, wt, top, group_off, pos, row, norm_in=norm_in, rstd_out=rstd)
+    assert torch.allclose(z.cpu().double(), z_ref, atol=2e-4 * float(z_ref.abs().max()))
+    assert torch.equal(idx.cpu().long()[sure], idx_ref[sure])
+    assert torch.allclose(wt.cpu().double()[sure], wt_ref[sure], atol=1e-4)
+    if unfinished:
+        assert torch.allclose(rstd.cpu().double(), rstd_ref[:, 0], rtol=1e-5)
+    # the sort: the same offsets as the sort kernel gives for these choices, every slot at a place of its expert's range
+    g2, p2, r2 = torch.empty_like(group_off), torch.empty_like(pos), torch.empty_like(row)
+    ops.moe_sort(idx, E, g2, p2, r2)
+    assert torch.equal(group_off, g2)
+    flat, off, pl, rw = idx.cpu().view(-1).tolist(), group_off.cpu().tolist(), pos.cpu().tolist(), row.cpu().tolist()
+    assert sorted(pl) == list(range(T * top))
+    for i, e in enumerate(flat):
+        assert off[e] <= pl[i] < off[e + 1] and rw[pl[i]] == i // top
+
+
 def test_router_ties_take_the_lower_expert(cuda_device):
     x = torch.ones(3, 8, device="cuda")
     w = torch.zeros(6, 8, device="cuda")
