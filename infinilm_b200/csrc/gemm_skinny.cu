@@ -65,7 +65,8 @@ __device__ __forceinline__ void gs_norm_finish(float* rstd_s, const float (&pv)[
 }
 
 // NT: 8-row groups of x (1: M <= 8, 2: M <= 16). GLU: 0 plain, 1 SwiGLU (W holds N gate rows, then N up rows). U: blocks in flight.
-template <int NT, int GLU, int U, typename TO>
+// NRM: the activations may come without their norm's 1/rms (`ni`); the SwiGLU form always can, the plain form as a variant of its own.
+template <int NT, int GLU, int U, typename TO, bool NRM = (GLU != 0)>
 __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
                                                                     const __nv_bfloat16* __restrict__ W, int ldw, TO* __restrict__ out,
                                                                     int ldo, const float* __restrict__ bias, float alpha, int M, int N, int K,
@@ -88,7 +89,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __n
         }
     il_pdl_begin();
     float pv[NT][8];
-    if (GLU) gs_norm_fetch<NT>(pv, ni, M, warp, lane);
+    if (NRM) gs_norm_fetch<NT>(pv, ni, M, warp, lane);
     const __nv_bfloat16* xrow[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) xrow[t] = (t * 8 + r < M) ? x + (size_t)(t * 8 + r) * ldx : nullptr;
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __n
                 }
     }
     il_pdl_tail();
-    if (GLU) gs_norm_finish<NT>(rstd_s, pv, ni, warp, lane);
+    if (NRM) gs_norm_finish<NT>(rstd_s, pv, ni, warp, lane);
 #pragma unroll
     for (int s = 0; s < NW; ++s)
 #pragma unroll
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __n
             s0 += part[w][0][t][nl][mc];
             if (GLU) s1 += part[w][0][t][nl + 8][mc];
         }
-        const float an = GLU ? __fmul_rn(alpha, rstd_s[m]) : alpha;     // the norm's 1/rms, where the activations came without it
+        const float an = NRM ? __fmul_rn(alpha, rstd_s[m]) : alpha;     // the norm's 1/rms, where the activations came without it
         float y = __fmaf_rn(an, s0, bias ? bias[n] : 0.f);      // spelled out as one fused multiply-add: the same bits from every build of this line
         if (GLU) {
             const float u = __fmaf_rn(an, s1, bias ? bias[N + n] : 0.f);
@@ -160,23 +161,23 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __n
     }
 }
 
-template <int NT, int GLU, typename TO>
+template <int NT, int GLU, typename TO, bool NRM = (GLU != 0)>
 static cudaError_t gs_launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, const float* bias, float alpha, int M, int N,
                       int K, cudaStream_t stream, const GsNormIn& ni = GsNormIn{nullptr, 0, 0.f, 0.f}) {
     constexpr int U = NT == 1 ? 8 : 4;
     constexpr int ROWS = GLU ? 8 : 16;
-    return il_launch(gemm_skinny_kernel<NT, GLU, U, TO>, dim3((N + ROWS - 1) / ROWS), dim3(GS_WARPS * 32), 0, stream,
+    return il_launch(gemm_skinny_kernel<NT, GLU, U, TO, NRM>, dim3((N + ROWS - 1) / ROWS), dim3(GS_WARPS * 32), 0, stream,
               (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (TO*)out, ldo, bias, alpha, M, N, K, ni);
 }
 
 // glu = 1: W is [2N, K] (N gate rows, then N up rows), bias [2N], out[M,N] = silu(alpha*x.Wg^T + bg) * (alpha*x.Wu^T + bu).
-// norm_partial (glu only, may be null): x is residual * norm weight and still wants its 1/rms, from these sums of squares
+// norm_partial (may be null; without glu: bfloat16 out): x is residual * norm weight and still wants its 1/rms, from these sums of squares
 // [M][n_partial] (n_partial <= 256, H = the width they were summed over).
 IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int out_kind, int ldo, const float* bias,
                              float alpha, int M, int N, int K, int glu, const float* norm_partial, int n_partial, int norm_h,
                              float norm_eps, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return IL_OK;
-    if (norm_partial && (!glu || n_partial <= 0 || n_partial > GS_NORM_MAX_PARTIALS || norm_h <= 0)) return IL_UNSUPPORTED;
+    if (norm_partial && (n_partial <= 0 || n_partial > GS_NORM_MAX_PARTIALS || norm_h <= 0 || (!glu && out_kind != IL_BF16))) return IL_UNSUPPORTED;
     const GsNormIn ni{norm_partial, n_partial, norm_partial ? 1.f / (float)norm_h : 0.f, norm_eps};
     if (M > 16 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K || ldo < N) return IL_UNSUPPORTED;
     if (out_kind != IL_F32 && out_kind != IL_BF16) return IL_BAD_ARG;
@@ -184,10 +185,12 @@ IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, voi
     cudaError_t e;
     if (M <= 8) {
         if (glu) e = gs_launch<1, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (norm_partial) e = gs_launch<1, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (out_kind == IL_BF16) e = gs_launch<1, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
         else e = gs_launch<1, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     } else {
         if (glu) e = gs_launch<2, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (norm_partial) e = gs_launch<2, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (out_kind == IL_BF16) e = gs_launch<2, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
         else e = gs_launch<2, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     }

@@ -335,6 +335,52 @@ __global__ void moe_combine_kernel(const TA* y, const int* pos_of_slot, const fl
     }
 }
 
+// The combine as the last step of a branch of a few bfloat16 rows: the token's sum, rounded to bfloat16 as the branch is
+// when it is passed on, goes into the float32 residual (resid += bscale * branch), and what the next RMSNorm needs is
+// left for the product that follows: xw = resid * norm weight (bfloat16) and, per block of 16 columns, the sum of the
+// residual's squares (sumsq [T][n_partial]). Four columns a thread: four neighbouring lanes own a block of 16.
+__global__ void moe_combine_resid_kernel(const __nv_bfloat16* y, const int* pos_of_slot, const float* wt, const __nv_bfloat16* shared_rows, int H, int top,
+                                         float* resid, float bscale, const void* __restrict__ norm_w, int nw_kind, __nv_bfloat16* __restrict__ xw,
+                                         float* __restrict__ sumsq, int n_partial) {
+    __shared__ int sp[MOE_MAX_TOP];
+    __shared__ float sw[MOE_MAX_TOP];
+    const int t = blockIdx.x;
+    il_pdl_begin();
+    if (threadIdx.x < top) {
+        sp[threadIdx.x] = pos_of_slot[(size_t)t * top + threadIdx.x];
+        sw[threadIdx.x] = wt[(size_t)t * top + threadIdx.x];
+    }
+    __syncthreads();
+    for (int base = 0; base < H; base += blockDim.x * 4) {
+        const int h = base + threadIdx.x * 4;
+        float sq = 0.f;
+        if (h < H) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const float4 v = ld4c(y + (size_t)sp[k] * H + h);
+                const float w = sw[k];
+                s.x = fmaf(w, v.x, s.x), s.y = fmaf(w, v.y, s.y), s.z = fmaf(w, v.z, s.z), s.w = fmaf(w, v.w, s.w);
+            }
+            if (shared_rows) {
+                const float4 v = ld4c(shared_rows + (size_t)t * H + h);
+                s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+            }
+            float4 r = *reinterpret_cast<const float4*>(resid + (size_t)t * H + h);
+            r.x = fmaf(bscale, __bfloat162float(__float2bfloat16_rn(s.x)), r.x);
+            r.y = fmaf(bscale, __bfloat162float(__float2bfloat16_rn(s.y)), r.y);
+            r.z = fmaf(bscale, __bfloat162float(__float2bfloat16_rn(s.z)), r.z);
+            r.w = fmaf(bscale, __bfloat162float(__float2bfloat16_rn(s.w)), r.w);
+            *reinterpret_cast<float4*>(resid + (size_t)t * H + h) = r;
+            st4c(xw + (size_t)t * H + h, make_float4(r.x * il_load_any(norm_w, nw_kind, h), r.y * il_load_any(norm_w, nw_kind, h + 1),
+                                                     r.z * il_load_any(norm_w, nw_kind, h + 2), r.w * il_load_any(norm_w, nw_kind, h + 3)));
+            sq = (r.x * r.x + r.y * r.y) + (r.z * r.z + r.w * r.w);
+        }
+        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+        if (h < H && (threadIdx.x & 3) == 0) sumsq[(size_t)t * n_partial + (h >> 4)] = sq;
+    }
+}
+
 // out[p] = x[rows[p]]: the rows of the tokens in the order of the sorted slots, for a product that wants them contiguous.
 template <typename TA>
 __global__ void gather_rows_kernel(const TA* x, int ldx, const int* rows, TA* __restrict__ out, int H) {
@@ -348,6 +394,20 @@ __global__ void gather_rows_kernel(const TA* x, int ldx, const int* rows, TA* __
     } else {
         for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
     }
+}
+
+// The combine of a few bfloat16 rows with the residual add and the next norm's inputs (see moe_combine_resid_kernel).
+// H a multiple of 4, sumsq [T][ceil(H / 16)].
+IL_EXPORT int il_moe_combine_resid(const void* y, const int* pos_of_slot, const float* wt, const void* shared_rows, int T, int H, int top, float* resid,
+                                   float bscale, const void* norm_w, int nw_kind, void* xw, float* sumsq, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (H <= 0 || top <= 0 || top > MOE_MAX_TOP || !resid || !norm_w || !xw || !sumsq) return IL_BAD_ARG;
+    if (H % 4 || ((uintptr_t)y & 15) || ((uintptr_t)shared_rows & 15) || ((uintptr_t)resid & 15) || ((uintptr_t)xw & 7)) return IL_UNSUPPORTED;
+    const int threads = H >= 2048 ? 512 : H >= 1024 ? 256 : 128;
+    IL_LAUNCH(moe_combine_resid_kernel, T, threads, 0, stream, (const __nv_bfloat16*)y, pos_of_slot, wt, (const __nv_bfloat16*)shared_rows, H, top, resid,
+              bscale, norm_w, nw_kind, (__nv_bfloat16*)xw, sumsq, (H + 15) / 16);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
 }
 
 IL_EXPORT int il_gather_rows(const void* x, int act_kind, int ldx, const int* rows, void* out, int n_rows, int H, cudaStream_t stream) {

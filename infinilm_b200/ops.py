@@ -456,7 +456,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
                 bias: Optional[torch.Tensor] = None, glu: bool = False, norm_in: Optional[NormedInput] = None) -> None:
     """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) for M <= 16 bfloat16 rows; out bfloat16 or float32.
     glu: w is [2N,K] (gate rows, then up rows) and out[M,N] = silu(gate) * up.
-    norm_in (glu only): x is `norm_in.xw`, and the results are divided by the rms that its sums give."""
+    norm_in (with glu, or with a bfloat16 out): x is `norm_in.xw`, and the results are divided by the rms that its sums give."""
     _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0] // 2 if glu else w.shape[0]
@@ -466,8 +466,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
         raise KernelError("gemm_skinny: innermost dimension must be contiguous")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0]):
         raise KernelError("gemm_skinny: bias float32, one per weight row")
-    if norm_in is not None and not glu:
-        raise KernelError("gemm_skinny: norm_in goes with glu=True (or gemm_skinny_rope)")
+    if norm_in is not None and not glu and out.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny: norm_in goes with glu=True or a bfloat16 out")
     f = _fn("gemm_skinny", "il_gemm_skinny", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
                                               _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_float,
                                               _c_void_p])
@@ -845,6 +845,33 @@ def moe_combine(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, sh
         _contig("shared_rows", shared_rows)
     f = _fn("moe", "il_moe_combine", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(y), kind_of(y.dtype), _ptr(pos_of_slot), _ptr(wt), _ptr(shared_rows), _ptr(out), T, H, top, _stream()), "moe_combine")
+
+
+def moe_combine_resid(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, shared_rows: Optional[torch.Tensor], resid: torch.Tensor,
+                      branch_scale: float, norm_weight: torch.Tensor, eps: float, xw: torch.Tensor, sumsq: torch.Tensor) -> NormedInput:
+    """`moe_combine` as the last step of a branch of a few bfloat16 rows, with the residual add and the next RMSNorm's
+    inputs: resid (float32 [T,H], in place) += branch_scale * bf16(sum); xw = resid * norm_weight; sumsq[t][b] = sum of
+    resid[t]^2 over columns 16b..16b+15. Returns what the next product needs to finish the norm."""
+    _need_cuda(y, pos_of_slot, wt, shared_rows, resid, norm_weight, xw, sumsq)
+    T, top = wt.shape
+    H = resid.shape[1]
+    nb = (H + 15) // 16
+    if y.dtype != torch.bfloat16 or y.shape[1] != H or y.shape[0] < T * top or H % 4:
+        raise KernelError("moe_combine_resid: y bfloat16 [T * top, H], H a multiple of 4")
+    if shared_rows is not None and (shared_rows.dtype != torch.bfloat16 or tuple(shared_rows.shape) != (T, H)):
+        raise KernelError("moe_combine_resid: shared_rows bfloat16 [T, H]")
+    if resid.dtype != torch.float32 or tuple(resid.shape) != (T, H) or xw.dtype != torch.bfloat16 or tuple(xw.shape) != (T, H):
+        raise KernelError("moe_combine_resid: resid float32 [T,H], xw bfloat16 [T,H]")
+    if sumsq.dtype != torch.float32 or tuple(sumsq.shape) != (T, nb) or nb > NORM_MAX_BLOCKS or norm_weight.numel() != H:
+        raise KernelError("moe_combine_resid: sumsq float32 [T, ceil(H/16) <= 256], norm_weight [H]")
+    _contig("y", y), _contig("wt", wt), _contig("resid", resid), _contig("xw", xw), _contig("sumsq", sumsq), _contig("norm_weight", norm_weight)
+    if shared_rows is not None:
+        _contig("shared_rows", shared_rows)
+    f = _fn("moe", "il_moe_combine_resid", [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p,
+                                            _c_int, _c_void_p, _c_void_p, _c_void_p])
+    _check(f(_ptr(y), _ptr(pos_of_slot), _ptr(wt), _ptr(shared_rows), T, H, top, _ptr(resid), branch_scale, _ptr(norm_weight),
+             kind_of(norm_weight.dtype), _ptr(xw), _ptr(sumsq), _stream()), "moe_combine_resid")
+    return NormedInput(xw, sumsq, H, eps)
 
 
 def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, group_off: Optional[torch.Tensor] = None,

@@ -87,13 +87,20 @@ class LatentAttention(Mixer):
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed("paged_kv", n_kv_heads=1, head_dim=self.r, window=self.window)
 
+    def accepts_normed(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden)
+
     def fuses_tail(self, T):
         return self.dtype == torch.bfloat16 and ops.skinny_resid_ok(T, self.nh * self.e, self.hidden)
 
     def forward(self, x, ctx, cache, tail=None):
         T, H = x.shape[0], self.nh
         ws, dt = ctx.ws, self.dtype
-        proj = self.down(x, ws.rows("lat_down", T, self.n_down, dt))
+        if isinstance(x, ops.NormedInput):       # rows whose norm the branch before left unfinished: this product divides by the rms
+            proj = ws.rows("lat_down", T, self.n_down, dt)
+            ops.gemm_skinny(x.xw, self.down.weight, proj, self.down.alpha, self.down.bias, norm_in=x)
+        else:
+            proj = self.down(x, ws.rows("lat_down", T, self.n_down, dt))
         cq = ws.rows("lat_cq", T, self.qr, dt)
         ops.latent_norm_store(proj, 0, self.qr, self.qr, self.r, self.nq, self.nkv, self.eps, cq, None, ctx.tok_pos, ctx.tok_entry,
                               cache.block_table, cache.storage if cache.writable else None, cache.page_size)

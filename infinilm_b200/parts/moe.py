@@ -93,7 +93,12 @@ class RoutedExperts(FeedForward):
                 and T * self.top < self.LIBRARY_FROM_SLOTS and T < self.ROUTER_PRODUCT_FROM
                 and (self.shared is None or self.shared.accepts_normed(T)))
 
-    def forward(self, x, ctx):
+    def fuses_tail(self, T):
+        """A few rows: the combine adds into the residual and leaves the next norm's inputs (it is the branch's last step)."""
+        return (self.dtype == torch.bfloat16 and 0 < T <= ops.SKINNY_MAX_ROWS and self.hidden % 4 == 0
+                and (self.hidden + 15) // 16 <= ops.NORM_MAX_BLOCKS)
+
+    def forward(self, x, ctx, tail=None):
         T, W, k = x.shape[0], self.hidden, self.top
         ws, dt, n_slots = ctx.ws, self.dtype, x.shape[0] * self.top
         idx = ws.rows("moe_idx", T, k, torch.int32)
@@ -133,6 +138,9 @@ class RoutedExperts(FeedForward):
                              glu=True, row_scale=rstd)
             ops.gemm_grouped(act, self.w_down, y, group_off=group_off, n_rows=n_slots)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        if tail is not None:
+            return ops.moe_combine_resid(y, pos_of_slot, wt, shared, tail.resid, tail.scale, tail.norm.weight, tail.norm.eps,
+                                         ws.rows("xw_ffn", T, W, dt), ws.rows("sumsq_ffn", T, (W + 15) // 16, torch.float32))
         out = ws.rows("moe_out", T, W, dt)
         ops.moe_combine(y, pos_of_slot, wt, shared, out)
         return out

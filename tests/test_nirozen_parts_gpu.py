@@ -286,6 +286,36 @@ def test_routed_feed_forward_takes_rows_whose_norm_is_unfinished(cuda_device, na
     close(got, ref, "bfloat16", f"T={T}")
 
 
+@pytest.mark.parametrize("T,W,top,shared", [(1, 96, 2, True), (8, 2048, 6, True), (16, 100, 3, False), (5, 4096, 1, True)])
+def test_combine_that_ends_the_branch(cuda_device, T, W, top, shared):
+    """The combine of a few rows with the residual add and the next norm's inputs, and the plain weight-streaming product
+    that reads them: together they must give what add + norm + product give."""
+    g = torch.Generator().manual_seed(T + W)
+    n_slots = T * top
+    y = torch.randn(n_slots + 3, W, generator=g).bfloat16()
+    pos = torch.randperm(n_slots, generator=g).int()
+    wt = torch.softmax(torch.randn(T, top, generator=g), -1)
+    sh = torch.randn(T, W, generator=g).bfloat16() if shared else None
+    resid = torch.randn(T, W, generator=g) * 3
+    nw = 1.0 + torch.randn(W, generator=g) * 0.1
+    eps, scale = 1e-5, 0.7
+    branch = (wt.double()[:, :, None] * y.double()[pos.long().view(T, top)]).sum(1) + (sh.double() if shared else 0.0)
+    new_resid = resid.double() + scale * branch.bfloat16().double()
+    r = resid.cuda().clone()
+    xw = torch.empty(T, W, dtype=torch.bfloat16, device="cuda")
+    sumsq = torch.empty(T, (W + 15) // 16, device="cuda")
+    ni = ops.moe_combine_resid(y.cuda(), pos.cuda(), wt.cuda(), sh.cuda() if shared else None, r, scale, nw.cuda(), eps, xw, sumsq)
+    assert torch.allclose(r.cpu().double(), new_resid, atol=2e-2, rtol=0)            # a sum may round to the neighbouring bfloat16
+    assert torch.allclose(sumsq.sum(1).cpu().double(), (r.cpu().double() ** 2).sum(1), rtol=1e-5)
+    close(xw, r.cpu().double() * nw.double(), "bfloat16")
+    if W % 8 == 0:
+        wd = (torch.randn(40, W, generator=g) * 0.1).bfloat16()
+        out = torch.empty(T, 40, dtype=torch.bfloat16, device="cuda")
+        ops.gemm_skinny(ni.xw, wd.cuda(), out, 1.0, None, norm_in=ni)
+        normed = xw.cpu().double() * torch.rsqrt((r.cpu().double() ** 2).mean(-1, keepdim=True) + eps)
+        close(out, normed @ wd.double().t(), "bfloat16")
+
+
 # ---- attention with a sink, kernel by kernel ---------------------------------------------------------------------
 def _sink_case(nh, hd, starts, qlens, seed, far=None):
     """Entries with `starts[i]` cached positions and `qlens[i]` new ones over a cache whose K and V planes hold the same
