@@ -90,7 +90,7 @@ class CacheGroup:
     """Run-order entries whose caches have the same geometry and policy share page ids:
     one block table per (request, group), one storage tensor per entry."""
     need: CacheNeed
-    entries: List[int]                            # run-order indices that own a cache in this group
+    entries: List[object]                         # owners (run-order index i, or (i, j) for the j-th need of entry i) with a cache in this group
     pool: Optional[PagePool] = None               # paged_kv groups
     storage: Dict[int, object] = field(default_factory=dict)   # run-order index -> device tensor
     tma_maps: Dict[int, object] = field(default_factory=dict)  # run-order index -> tensor map of its storage (or absent)
@@ -190,8 +190,9 @@ class CacheManager:
 
     def __init__(self, needs: Sequence[Optional[CacheNeed]], page_size: int, num_pages: int, max_seqs: int,
                  device=None, dtype=None, pages_per_group: Optional[Dict[int, int]] = None):
-        """`needs[i]` is what run-order entry i keeps (None: nothing). `num_pages` pages are made
-        for every paged group (or `pages_per_group[g]`); `max_seqs` bounds live requests."""
+        """`needs[i]` is what run-order entry i keeps: None (nothing), a `CacheNeed`, or a tuple of them (pages and a
+        state, several states) - the j-th of a tuple is known here as owner (i, j), a single one as owner i.
+        `num_pages` pages are made for every paged group (or `pages_per_group[g]`); `max_seqs` bounds live requests."""
         self.page_size, self.max_seqs = int(page_size), int(max_seqs)
         if self.page_size <= 0 or (self.page_size & (self.page_size - 1)):
             raise ValueError("page_size must be a power of two")
@@ -203,16 +204,19 @@ class CacheManager:
         self.groups: List[CacheGroup] = []
         self.group_of_entry: Dict[int, int] = {}
         by_key: Dict[Tuple, int] = {}
-        for i, need in enumerate(needs):
-            if need is None:
+        for i, need_i in enumerate(needs):
+            if need_i is None:
                 continue
-            k = need.group_key()
-            if k not in by_key:
-                by_key[k] = len(self.groups)
-                self.groups.append(CacheGroup(need, []))
-            g = by_key[k]
-            self.groups[g].entries.append(i)
-            self.group_of_entry[i] = g
+            several = isinstance(need_i, (tuple, list))
+            for j, need in enumerate(need_i if several else (need_i,)):
+                owner = (i, j) if several else i
+                k = need.group_key()
+                if k not in by_key:
+                    by_key[k] = len(self.groups)
+                    self.groups.append(CacheGroup(need, []))
+                g = by_key[k]
+                self.groups[g].entries.append(owner)
+                self.group_of_entry[owner] = g
         for g, grp in enumerate(self.groups):
             if grp.need.kind == "paged_kv":
                 grp.pool = PagePool((pages_per_group or {}).get(g, num_pages))

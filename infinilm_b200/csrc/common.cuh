@@ -72,6 +72,19 @@ __device__ __forceinline__ float il_block_max(float v, float* sh) {
 // depend on which of the two computed it. The float32 path keeps expf and a true division.
 __device__ __forceinline__ float il_silu_mul_fast(float g, float u) { return __fmul_rn(__fdividef(g, __fadd_rn(1.f, __expf(-g))), u); }
 
+// gelu_tanh(g) * u with gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))): the other gate of a gated feed-forward.
+// 0.5 (1 + tanh(a)) = 1 / (1 + exp(-2a)); the bfloat16 path takes the fast exponential and division, as the SiLU form does.
+__device__ __forceinline__ float il_gelu_tanh_mul_fast(float g, float u) {
+    const float a = 0.7978845608028654f * __fmaf_rn(0.044715f * g * g, g, g);
+    return __fmul_rn(__fdividef(g, __fadd_rn(1.f, __expf(-2.f * a))), u);
+}
+__device__ __forceinline__ float il_gelu_tanh_mul(float g, float u) {
+    const float a = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.f + tanhf(a)) * u;
+}
+// The gate of a gated feed-forward by number: 1 SiLU, 2 the tanh form of GELU.
+enum { IL_ACT_SILU = 1, IL_ACT_GELU_TANH = 2 };
+
 // ---- programmatic dependent launch --------------------------------------------------------------
 // Kernels of the decode path are launched so that the next kernel in the stream may become resident
 // while this one drains (INFINILM_B200_PDL=0 turns it off). A kernel waits for its predecessor to have

@@ -84,6 +84,7 @@ enum { GM_PLAIN = 0, GM_GLU = 1 };
 struct GmParams {
     int M, N, K;                                  // N: output columns (SwiGLU: the intermediate size; W has 2N rows)
     int mode, n_acc;                              // accumulators per unit: 1 plain, 2 SwiGLU (gate, up)
+    int act;                                      // the gate of the SwiGLU form: IL_ACT_SILU or IL_ACT_GELU_TANH
     int NB, n_bb;                                 // activation rows per unit (a multiple of 16), blocks of them
     int n_issuers;                                // threads that issue products, each into an accumulator of its own
     int tma3d;                                    // the tensor maps are the three-dimensional ones (K a multiple of 64)
@@ -274,7 +275,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_mid_kernel(const __grid_co
                 gm_ld16(taddr + p.NB + j0, vu);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 float y[16];
-                if (p.mode == GM_GLU) {
+                if (p.mode == GM_GLU && p.act == IL_ACT_GELU_TANH) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        y[j] = il_gelu_tanh_mul_fast(__fmaf_rn(p.alpha, __uint_as_float(vg[j]), bg), __fmaf_rn(p.alpha, __uint_as_float(vu[j]), bu));
+                } else if (p.mode == GM_GLU) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         y[j] = il_silu_mul_fast(__fmaf_rn(p.alpha, __uint_as_float(vg[j]), bg), __fmaf_rn(p.alpha, __uint_as_float(vu[j]), bu));
@@ -388,7 +393,7 @@ static int gm_pick_nb(int Mp, int n_tiles, int n_sm) {
 
 IL_EXPORT int il_gemm_mid_max_rows() { return GM_MAX_ROWS; }
 
-// glu = 1: W is [2N, K] (N gate rows, then N up rows), bias [2N], out[M,N] = silu(alpha*x.Wg^T + bg) * (alpha*x.Wu^T + bu).
+// glu = 1: W is [2N, K] (N gate rows, then N up rows), bias [2N], out[M,N] = silu(alpha*x.Wg^T + bg) * (alpha*x.Wu^T + bu); glu = 2: gelu_tanh for silu.
 // nb: activation rows per unit, bm_want: weight rows per tile, 64 or 128 (0: chosen here).
 IL_EXPORT int il_gemm_mid(const void* x, int ldx, const void* W, int ldw, void* out, int out_kind, int ldo, const float* bias,
                           float alpha, int M, int N, int K, int glu, int nb, int bm_want, int* status, cudaStream_t stream) {
@@ -401,7 +406,7 @@ IL_EXPORT int il_gemm_mid(const void* x, int ldx, const void* W, int ldw, void* 
     const int Mp = (M + 15) & ~15;
 
     GmParams p;
-    p.M = M; p.N = N; p.K = K; p.mode = glu ? GM_GLU : GM_PLAIN; p.n_acc = glu ? 2 : 1;
+    p.M = M; p.N = N; p.K = K; p.mode = glu ? GM_GLU : GM_PLAIN; p.n_acc = glu ? 2 : 1; p.act = glu == 2 ? IL_ACT_GELU_TANH : IL_ACT_SILU;
     // tiles of 128 rows where that still gives (nearly) every SM a unit at whole activation blocks: a product of M = 64
     // covers 2 KB of weights and the tensor pipe takes some 80 clocks for it, which holds an SM to about 50 GB/s
     const int bm = bm_want > 0 ? bm_want : ((long long)((N + 127) / 128) * 100 >= (long long)n_sm * 85 ? 128 : 64);

@@ -64,7 +64,7 @@ __device__ __forceinline__ void gs_norm_finish(float* rstd_s, const float (&pv)[
     }
 }
 
-// NT: 8-row groups of x (1: M <= 8, 2: M <= 16). GLU: 0 plain, 1 SwiGLU (W holds N gate rows, then N up rows). U: blocks in flight.
+// NT: 8-row groups of x (1: M <= 8, 2: M <= 16). GLU: 0 plain, 1 SwiGLU, 2 the same with the tanh form of GELU as the gate (W holds N gate rows, then N up rows). U: blocks in flight.
 // NRM: the activations may come without their norm's 1/rms (`ni`); the SwiGLU form always can, the plain form as a variant of its own.
 template <int NT, int GLU, int U, typename TO, bool NRM = (GLU != 0)>
 __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __n
         float y = __fmaf_rn(an, s0, bias ? bias[n] : 0.f);      // spelled out as one fused multiply-add: the same bits from every build of this line
         if (GLU) {
             const float u = __fmaf_rn(an, s1, bias ? bias[N + n] : 0.f);
-            y = il_silu_mul_fast(y, u);
+            y = GLU == 2 ? il_gelu_tanh_mul_fast(y, u) : il_silu_mul_fast(y, u);
         }
         gs_store<TO>(out + (size_t)m * ldo + n, y);
     }
@@ -170,7 +170,8 @@ static cudaError_t gs_launch(const void* x, int ldx, const void* W, int ldw, voi
               (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (TO*)out, ldo, bias, alpha, M, N, K, ni);
 }
 
-// glu = 1: W is [2N, K] (N gate rows, then N up rows), bias [2N], out[M,N] = silu(alpha*x.Wg^T + bg) * (alpha*x.Wu^T + bu).
+// glu = 1: W is [2N, K] (N gate rows, then N up rows), bias [2N], out[M,N] = silu(alpha*x.Wg^T + bg) * (alpha*x.Wu^T + bu);
+// glu = 2: the same with gelu_tanh in place of silu.
 // norm_partial (may be null; without glu: bfloat16 out): x is residual * norm weight and still wants its 1/rms, from these sums of squares
 // [M][n_partial] (n_partial <= 256, H = the width they were summed over).
 IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int out_kind, int ldo, const float* bias,
@@ -184,12 +185,14 @@ IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, voi
     if (glu && out_kind != IL_BF16) return IL_UNSUPPORTED;
     cudaError_t e;
     if (M <= 8) {
-        if (glu) e = gs_launch<1, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        if (glu == 2) e = gs_launch<1, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (glu) e = gs_launch<1, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (norm_partial) e = gs_launch<1, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (out_kind == IL_BF16) e = gs_launch<1, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
         else e = gs_launch<1, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     } else {
-        if (glu) e = gs_launch<2, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        if (glu == 2) e = gs_launch<2, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (glu) e = gs_launch<2, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (norm_partial) e = gs_launch<2, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (out_kind == IL_BF16) e = gs_launch<2, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
         else e = gs_launch<2, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);

@@ -1,5 +1,6 @@
 // Residual add fused with RMSNorm.
-//   x = resid[r] + branch_scale * branch[r] + vec   (branch may be absent; vec, one f32 vector added to every row, too)
+//   x = resid[r] + branch_scale * branch[r] + vec   (branch may be absent; vec too: f32, one vector added to every row, or -
+//                                                    vec_stride = H - a row of its own for every row of resid)
 //   resid[r] = x                              (kept in f32; skipped when a row list is given)
 //   out[i]  = x / sqrt(mean(x^2) + eps) * w
 // Sum of squares, rsqrt and the scaling are f32; one block per row with a fixed thread count,
@@ -9,13 +10,14 @@
 template <typename TA>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ branch, float bscale,
                                    const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ out,
-                                   const int* __restrict__ rows, int H, const float* __restrict__ vec) {
+                                   const int* __restrict__ rows, int H, const float* __restrict__ vec, int vec_stride) {
     extern __shared__ float xs[];
     __shared__ float red[32];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
     float* rr = resid + (size_t)r * H;
     const TA* br = branch ? branch + (size_t)r * H : nullptr;
+    if (vec) vec += (size_t)r * vec_stride;
     float ss = 0.f;
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         float x = rr[h];
@@ -52,7 +54,7 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
 template <typename TA, int MAXV>
 __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* resid, const TA* branch, float bscale,
                                                               const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ out,
-                                                              const int* __restrict__ rows, int H, const float* __restrict__ vec) {
+                                                              const int* __restrict__ rows, int H, const float* __restrict__ vec, int vec_stride) {
     __shared__ float red[32];
     const int i = blockIdx.x;
     const int nv = H >> 2;                        // float4 groups in a row
@@ -89,6 +91,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* resid, cons
         }
     }
     if (vec) {
+        vec += (size_t)r * vec_stride;
 #pragma unroll
         for (int k = 0; k < MAXV; ++k) {
             const int v = threadIdx.x + k * 256;
@@ -118,25 +121,25 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* resid, cons
 
 template <typename TA>
 static int launch_vec(float* resid, const void* branch, float bscale, const void* w, int w_kind, float eps, void* out,
-                      const int* rows, int n_rows, int H, const float* vec, cudaStream_t stream) {
+                      const int* rows, int n_rows, int H, const float* vec, int vec_stride, cudaStream_t stream) {
     const int nv = H >> 2;
     if (nv <= 256 * 2)
-        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 2>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 2>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec, vec_stride);
     else if (nv <= 256 * 4)
-        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 4>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 4>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec, vec_stride);
     else
-        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 8>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 8>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H, vec, vec_stride);
     return 0;
 }
 
 IL_EXPORT int il_add_rmsnorm(float* resid, const void* branch, float bscale, const void* w, int w_kind,
                              float eps, void* out, int act_kind, const int* rows, int n_rows, int H,
-                             const float* vec, cudaStream_t stream) {
+                             const float* vec, int vec_stride, cudaStream_t stream) {
     if (n_rows <= 0) return IL_OK;
     if (H <= 0) return IL_BAD_ARG;
     if (H % 4 == 0 && H <= 256 * 8 * 4 && (act_kind == IL_F32 || act_kind == IL_BF16)) {
-        if (act_kind == IL_F32) launch_vec<float>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, vec, stream);
-        else launch_vec<__nv_bfloat16>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, vec, stream);
+        if (act_kind == IL_F32) launch_vec<float>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, vec, vec_stride, stream);
+        else launch_vec<__nv_bfloat16>(resid, branch, bscale, w, w_kind, eps, out, rows, n_rows, H, vec, vec_stride, stream);
         IL_LAUNCH_CHECK();
         return IL_OK;
     }
@@ -145,10 +148,10 @@ IL_EXPORT int il_add_rmsnorm(float* resid, const void* branch, float bscale, con
     const int threads = 256;
     if (act_kind == IL_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(resid, (const float*)branch, bscale, w, w_kind, eps, (float*)out, rows, H, vec);
+        add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(resid, (const float*)branch, bscale, w, w_kind, eps, (float*)out, rows, H, vec, vec_stride);
     } else if (act_kind == IL_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(resid, (const __nv_bfloat16*)branch, bscale, w, w_kind, eps, (__nv_bfloat16*)out, rows, H, vec);
+        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(resid, (const __nv_bfloat16*)branch, bscale, w, w_kind, eps, (__nv_bfloat16*)out, rows, H, vec, vec_stride);
     } else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

@@ -1,0 +1,362 @@
+// Sequence mixers that carry a fixed-size state per request instead of (or beside) cached keys: a short causal
+// convolution over time with its last inputs as state, two linear recurrences over a matrix state per head (a decayed
+// outer-product sum, and the gated delta rule), a norm over groups of columns with a gate, a gate per head, and a soft cap.
+//
+// A step's rows are the tokens of its entries one after the other (entry e: rows qstart[e] .. qstart[e+1]-1); an entry
+// reads its state from slot read_slots[e] (slot 0 holds zeros: a request's first step) and leaves it in write_slots[e].
+// Every recurrence runs token by token in the order of the sequence, in float32, so what a token gets does not depend on
+// how the sequence was cut into steps or on what else is in the batch.
+#include "common.cuh"
+
+__device__ __forceinline__ float sm_silu(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sm_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float sm_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+#define SM_MAX_TAPS 16
+
+// ---- short convolution ----------------------------------------------------------------------------------------------
+// y[t, ch] = act( sum_j w[ch, j] * u[t - (taps-1) + j, ch] ), u before the step's first row from the state (its row i is
+// the input (taps-1-i) tokens before the step's first), zeros before the sequence's start (the zero slot).
+// Channels are read as segments of seg_in columns and written as segments of seg_out >= seg_in columns, the rest zero
+// (heads padded to a common size). One thread per (row, output column).
+template <typename TI, typename TO>
+__global__ void short_conv_kernel(const TI* __restrict__ x, int ldx, int x_off, const float* __restrict__ w, int taps,
+                                  const float* __restrict__ state, size_t slot_stride, int st_off, int st_ld,
+                                  const int* __restrict__ read_slots, const int* __restrict__ tok_entry,
+                                  const int* __restrict__ qstart, TO* __restrict__ out, int ldo, int out_off, int n_seg, int seg_in,
+                                  int seg_out, int act, int T) {
+    const int cols = n_seg * seg_out;
+    const size_t total = (size_t)T * cols;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / cols), oc = (int)(idx - (size_t)t * cols);
+        const int seg = oc / seg_out, within = oc - seg * seg_out;
+        TO* o = out + (size_t)t * ldo + out_off + oc;
+        if (within >= seg_in) {
+            *o = il_from_f<TO>(0.f);
+            continue;
+        }
+        const int ch = seg * seg_in + within;
+        const int e = tok_entry[t];
+        const int local = t - qstart[e];
+        const float* st = state + (size_t)read_slots[e] * slot_stride + st_off + ch;
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int s = local - (taps - 1) + j;
+            const float u = s >= 0 ? il_to_f(x[(size_t)(t - local + s) * ldx + x_off + ch]) : st[(size_t)(taps - 1 + s) * st_ld];
+            acc = fmaf(w[(size_t)ch * taps + j], u, acc);
+        }
+        *o = il_from_f<TO>(act == 1 ? sm_silu(acc) : acc);
+    }
+}
+
+// The state after the step: the last taps-1 inputs of each entry (older ones from the state it had). One thread per
+// (entry, channel) reads all it needs before it writes, so an entry may read and write the same slot.
+template <typename TI>
+__global__ void short_conv_state_kernel(const TI* __restrict__ x, int ldx, int x_off, int C, int taps, float* state,
+                                        size_t slot_stride, int st_off, int st_ld, const int* __restrict__ read_slots,
+                                        const int* __restrict__ write_slots, const int* __restrict__ qstart, int E) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= E * C) return;
+    const int e = idx / C, ch = idx - e * C;
+    const int q0 = qstart[e], n = qstart[e + 1] - q0;
+    if (n <= 0) return;
+    const float* rd = state + (size_t)read_slots[e] * slot_stride + st_off + ch;
+    float keep[SM_MAX_TAPS];
+    for (int i = 0; i < taps - 1; ++i) {
+        const int s = n - (taps - 1) + i;
+        keep[i] = s >= 0 ? il_to_f(x[(size_t)(q0 + s) * ldx + x_off + ch]) : rd[(size_t)(taps - 1 + s) * st_ld];
+    }
+    float* wr = state + (size_t)write_slots[e] * slot_stride + st_off + ch;
+    for (int i = 0; i < taps - 1; ++i) wr[(size_t)i * st_ld] = keep[i];
+}
+
+static inline int sm_grid(size_t total, int threads) {
+    size_t g = (total + threads - 1) / threads;
+    return (int)(g > 148 * 32 ? 148 * 32 : (g < 1 ? 1 : g));
+}
+
+IL_EXPORT int il_short_conv(const void* x, int x_kind, int ldx, int x_off, const float* w, int taps, const float* state,
+                            long long slot_stride, int st_off, int st_ld, const int* read_slots, const int* tok_entry,
+                            const int* qstart, void* out, int out_kind, int ldo, int out_off, int n_seg, int seg_in, int seg_out,
+                            int act, int T, cudaStream_t stream) {
+    if (T <= 0 || n_seg <= 0) return IL_OK;
+    if (taps < 1 || taps > SM_MAX_TAPS || seg_in <= 0 || seg_out < seg_in) return IL_BAD_ARG;
+    const int grid = sm_grid((size_t)T * n_seg * seg_out, 256);
+#define SC_ARGS ldx, x_off, w, taps, state, (size_t)slot_stride, st_off, st_ld, read_slots, tok_entry, qstart
+#define SC_TAIL ldo, out_off, n_seg, seg_in, seg_out, act, T
+    if (x_kind == IL_F32 && out_kind == IL_F32)
+        short_conv_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)x, SC_ARGS, (float*)out, SC_TAIL);
+    else if (x_kind == IL_BF16 && out_kind == IL_F32)
+        short_conv_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, SC_ARGS, (float*)out, SC_TAIL);
+    else if (x_kind == IL_BF16 && out_kind == IL_BF16)
+        short_conv_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, SC_ARGS, (__nv_bfloat16*)out, SC_TAIL);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+IL_EXPORT int il_short_conv_state(const void* x, int x_kind, int ldx, int x_off, int C, int taps, float* state, long long slot_stride,
+                                  int st_off, int st_ld, const int* read_slots, const int* write_slots, const int* qstart, int E,
+                                  cudaStream_t stream) {
+    if (E <= 0 || C <= 0 || taps <= 1) return IL_OK;
+    if (taps > SM_MAX_TAPS) return IL_BAD_ARG;
+    const int grid = (E * C + 255) / 256;
+    if (x_kind == IL_F32)
+        short_conv_state_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, ldx, x_off, C, taps, state, (size_t)slot_stride, st_off, st_ld,
+                                                                 read_slots, write_slots, qstart, E);
+    else if (x_kind == IL_BF16)
+        short_conv_state_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, x_off, C, taps, state, (size_t)slot_stride,
+                                                                         st_off, st_ld, read_slots, write_slots, qstart, E);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- preparing the gated delta rule's inputs -------------------------------------------------------------------------
+// q and k heads (float32, in place) become unit vectors: x / sqrt(sum x^2 + unit_eps), q also times q_scale; and per value
+// head beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias)), both float32 [T, H]. One warp per (row, q/k head),
+// then the same warps over the value heads.
+__global__ void delta_prep_kernel(float* qk, int ld, int q_off, int k_off, int G, int dim, float q_scale, float unit_eps,
+                                  const float* __restrict__ ab, int ld_ab, int b_off, int a_off, const float* __restrict__ A_log,
+                                  const float* __restrict__ dt_bias, float* __restrict__ beta, float* __restrict__ gdec, int H, int T) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int per_row = 2 * G;
+    if (warp >= T * per_row) return;
+    const int t = warp / per_row, j = warp - t * per_row;
+    const bool is_q = j < G;
+    float* v = qk + (size_t)t * ld + (is_q ? q_off + j * dim : k_off + (j - G) * dim);
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss += v[d] * v[d];
+    ss = il_warp_sum(ss);
+    const float r = (1.f / sqrtf(ss + unit_eps)) * (is_q ? q_scale : 1.f);
+    for (int d = lane; d < dim; d += 32) v[d] *= r;
+    if (j == 0)
+        for (int h = lane; h < H; h += 32) {
+            beta[(size_t)t * H + h] = sm_sigmoid(ab[(size_t)t * ld_ab + b_off + h]);
+            gdec[(size_t)t * H + h] = expf(-expf(A_log[h]) * sm_softplus(ab[(size_t)t * ld_ab + a_off + h] + dt_bias[h]));
+        }
+}
+
+IL_EXPORT int il_delta_prep(float* qk, int ld, int q_off, int k_off, int G, int dim, float q_scale, float unit_eps, const float* ab,
+                            int ld_ab, int b_off, int a_off, const float* A_log, const float* dt_bias, float* beta, float* gdec, int H,
+                            int T, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (G <= 0 || dim <= 0 || H <= 0) return IL_BAD_ARG;
+    const size_t warps = (size_t)T * 2 * G;
+    delta_prep_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, stream>>>(qk, ld, q_off, k_off, G, dim, q_scale, unit_eps, ab, ld_ab, b_off,
+                                                                        a_off, A_log, dt_bias, beta, gdec, H, T);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- recurrences over a matrix state --------------------------------------------------------------------------------
+// State S [dim, vdim] per (request, head), float32. A block owns `blockDim.x` columns of one head of one entry, one column a
+// thread, the column in shared memory (column c of row d at s[d * ncol + c]: no bank is shared). Tokens in order:
+//   MODE 0 (decayed sum):  S = decay_h S + k v^T;                               o = S^T q
+//   MODE 1 (delta rule):   S = g_t S;  u = beta_t (v - S^T k);  S = S + k u^T;   o = S^T q
+// q and k of SM_CHUNK tokens are staged in shared memory at a time. `in_act` 1: silu on q, k, v as they are read.
+// q/k head of value head h: h / (H / G).
+#define SM_CHUNK 8
+template <int MODE>
+__global__ void matrix_state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld_q,
+                                         int ld_k, int ld_v, int H, int G, int dim, int vdim, int in_act,
+                                         const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
+                                         float* state, size_t slot_stride, const int* __restrict__ read_slots,
+                                         const int* __restrict__ write_slots, const int* __restrict__ qstart, float* __restrict__ out,
+                                         int ldo) {
+    extern __shared__ float sm[];
+    const int ncol = blockDim.x;
+    float* S = sm;                                // [dim][ncol]
+    float* qs = sm + (size_t)dim * ncol;          // [SM_CHUNK][dim]
+    float* ks = qs + SM_CHUNK * dim;              // [SM_CHUNK][dim]
+    const int e = blockIdx.x, h = blockIdx.y, c = blockIdx.z * ncol + threadIdx.x;
+    const int q0 = qstart[e], n = qstart[e + 1] - q0;
+    if (n <= 0) return;
+    const int hq = h / (H / G);
+    const bool live = c < vdim;
+    const float* rd = state + (size_t)read_slots[e] * slot_stride + (size_t)h * dim * vdim;
+    for (int d = 0; d < dim; ++d) S[d * ncol + threadIdx.x] = live ? rd[(size_t)d * vdim + c] : 0.f;
+    const float dec = MODE == 0 ? decay[h] : 0.f;
+    for (int t0 = 0; t0 < n; t0 += SM_CHUNK) {
+        const int nt = min(SM_CHUNK, n - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * dim; i += ncol) {
+            const int tt = i / dim, d = i - tt * dim;
+            const size_t row = (size_t)(q0 + t0 + tt);
+            float a = q[row * ld_q + hq * dim + d], b = k[row * ld_k + hq * dim + d];
+            if (in_act) a = sm_silu(a), b = sm_silu(b);
+            qs[i] = a, ks[i] = b;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const size_t row = (size_t)(q0 + t0 + tt);
+            float vc = live ? v[row * ld_v + h * vdim + c] : 0.f;
+            if (in_act) vc = sm_silu(vc);
+            const float* qq = qs + tt * dim;
+            const float* kk = ks + tt * dim;
+            float o = 0.f;
+            if (MODE == 0) {
+                for (int d = 0; d < dim; ++d) {
+                    const float s = fmaf(dec, S[d * ncol + threadIdx.x], kk[d] * vc);
+                    S[d * ncol + threadIdx.x] = s;
+                    o = fmaf(s, qq[d], o);
+                }
+            } else {
+                const float g = gdec[row * H + h], bt = beta[row * H + h];
+                float sk = 0.f;
+                for (int d = 0; d < dim; ++d) {
+                    const float s = g * S[d * ncol + threadIdx.x];
+                    S[d * ncol + threadIdx.x] = s;
+                    sk = fmaf(s, kk[d], sk);
+                }
+                const float u = bt * (vc - sk);
+                for (int d = 0; d < dim; ++d) {
+                    const float s = fmaf(kk[d], u, S[d * ncol + threadIdx.x]);
+                    S[d * ncol + threadIdx.x] = s;
+                    o = fmaf(s, qq[d], o);
+                }
+            }
+            if (live) out[row * ldo + h * vdim + c] = o;
+        }
+    }
+    if (live) {
+        float* wr = state + (size_t)write_slots[e] * slot_stride + (size_t)h * dim * vdim;
+        for (int d = 0; d < dim; ++d) wr[(size_t)d * vdim + c] = S[d * ncol + threadIdx.x];
+    }
+}
+
+IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v, int H, int G,
+                                   int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
+                                   long long slot_stride, const int* read_slots, const int* write_slots, const int* qstart, int E,
+                                   float* out, int ldo, cudaStream_t stream) {
+    if (E <= 0) return IL_OK;
+    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1)) return IL_BAD_ARG;
+    if (mode == 0 ? !decay : (!beta || !gdec)) return IL_BAD_ARG;
+    int ncol = vdim >= 128 ? 128 : vdim > 32 ? 64 : 32;
+    size_t smem = ((size_t)dim * ncol + 2 * SM_CHUNK * dim) * sizeof(float);
+    while (smem > 200 * 1024 && ncol > 32) {
+        ncol >>= 1;
+        smem = ((size_t)dim * ncol + 2 * SM_CHUNK * dim) * sizeof(float);
+    }
+    if (smem > 200 * 1024) return IL_UNSUPPORTED;
+    const dim3 grid(E, H, (vdim + ncol - 1) / ncol);
+    if (mode == 0) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        matrix_state_scan_kernel<0><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        matrix_state_scan_kernel<1><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo);
+    }
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- a norm over groups of columns, times a gate -----------------------------------------------------------------------
+// out[t, j] = x[t, j] / sqrt(mean over j's group of x^2 + eps) * w[j % n_w] * act(gate[t, j]); groups of `group` columns;
+// act 0: sigmoid, 1: silu. x float32, the gate float32 or bfloat16, out float32 or bfloat16. One block per (row, group).
+template <typename TG, typename TO>
+__global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, const void* __restrict__ w, int w_kind, int n_w, float eps,
+                                       const TG* __restrict__ gate, int ldg, int g_off, int act, TO* __restrict__ out, int ldo, int group) {
+    __shared__ float red[32];
+    const int t = blockIdx.x, j0 = blockIdx.y * group;
+    const float* xr = x + (size_t)t * ldx + j0;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < group; j += blockDim.x) ss += xr[j] * xr[j];
+    ss = il_block_sum(ss, red);
+    const float r = 1.f / sqrtf(ss / (float)group + eps);
+    for (int j = threadIdx.x; j < group; j += blockDim.x) {
+        const float z = il_to_f(gate[(size_t)t * ldg + g_off + j0 + j]);
+        const float a = act == 0 ? sm_sigmoid(z) : sm_silu(z);
+        out[(size_t)t * ldo + j0 + j] = il_from_f<TO>(xr[j] * r * il_load_any(w, w_kind, (j0 + j) % n_w) * a);
+    }
+}
+
+IL_EXPORT int il_group_norm_gate(const float* x, int ldx, const void* w, int w_kind, int n_w, float eps, const void* gate, int gate_kind,
+                                 int ldg, int g_off, int act, void* out, int out_kind, int ldo, int group, int n_groups, int T,
+                                 cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (group <= 0 || n_groups <= 0 || n_w <= 0) return IL_BAD_ARG;
+    const int threads = group >= 256 ? 256 : group >= 128 ? 128 : 64;
+    const dim3 grid(T, n_groups);
+#define GN_ARGS x, ldx, w, w_kind, n_w, eps
+    if (gate_kind == IL_F32 && out_kind == IL_F32)
+        group_norm_gate_kernel<float, float><<<grid, threads, 0, stream>>>(GN_ARGS, (const float*)gate, ldg, g_off, act, (float*)out, ldo, group);
+    else if (gate_kind == IL_F32 && out_kind == IL_BF16)
+        group_norm_gate_kernel<float, __nv_bfloat16><<<grid, threads, 0, stream>>>(GN_ARGS, (const float*)gate, ldg, g_off, act, (__nv_bfloat16*)out, ldo, group);
+    else if (gate_kind == IL_BF16 && out_kind == IL_BF16)
+        group_norm_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>(GN_ARGS, (const __nv_bfloat16*)gate, ldg, g_off, act, (__nv_bfloat16*)out, ldo, group);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- one gate per head --------------------------------------------------------------------------------------------------
+// out[t, h * vdim + c] = y[t, h * hd + c] * sigmoid(gate[t, g_off + h]) for c < vdim <= hd (heads that were padded to hd
+// columns come out packed). Without a gate only the packing is done.
+template <typename TA>
+__global__ void head_gate_kernel(const TA* __restrict__ y, int ldy, int hd, const TA* __restrict__ gate, int ldg, int g_off,
+                                 TA* __restrict__ out, int ldo, int nh, int vdim, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int per = nh * vdim;
+        const int t = (int)(idx / per), j = (int)(idx - (size_t)t * per);
+        const int h = j / vdim, c = j - h * vdim;
+        const float s = gate ? sm_sigmoid(il_to_f(gate[(size_t)t * ldg + g_off + h])) : 1.f;
+        out[(size_t)t * ldo + j] = il_from_f<TA>(il_to_f(y[(size_t)t * ldy + h * hd + c]) * s);
+    }
+}
+
+IL_EXPORT int il_head_gate(const void* y, int kind, int ldy, int hd, const void* gate, int ldg, int g_off, void* out, int ldo, int nh,
+                           int vdim, int T, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (nh <= 0 || vdim <= 0 || vdim > hd) return IL_BAD_ARG;
+    const size_t total = (size_t)T * nh * vdim;
+    const int grid = sm_grid(total, 256);
+    if (kind == IL_F32)
+        head_gate_kernel<float><<<grid, 256, 0, stream>>>((const float*)y, ldy, hd, (const float*)gate, ldg, g_off, (float*)out, ldo, nh, vdim, total);
+    else if (kind == IL_BF16)
+        head_gate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)y, ldy, hd, (const __nv_bfloat16*)gate, ldg, g_off,
+                                                                  (__nv_bfloat16*)out, ldo, nh, vdim, total);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- a weighted sum of two branches: out = sa * a + sb * b, summed in float32 ------------------------------------------------
+template <typename TA>
+__global__ void scaled_sum_kernel(const TA* __restrict__ a, float sa, const TA* __restrict__ b, float sb, TA* __restrict__ out, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = il_from_f<TA>(fmaf(sa, il_to_f(a[idx]), sb * il_to_f(b[idx])));
+}
+
+IL_EXPORT int il_scaled_sum(const void* a, float sa, const void* b, float sb, void* out, int kind, long long total, cudaStream_t stream) {
+    if (total <= 0) return IL_OK;
+    const int grid = sm_grid((size_t)total, 256);
+    if (kind == IL_F32)
+        scaled_sum_kernel<float><<<grid, 256, 0, stream>>>((const float*)a, sa, (const float*)b, sb, (float*)out, (size_t)total);
+    else if (kind == IL_BF16)
+        scaled_sum_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, sa, (const __nv_bfloat16*)b, sb, (__nv_bfloat16*)out, (size_t)total);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- soft cap: y = cap * tanh(y / cap), float32 in place ------------------------------------------------------------------
+__global__ void softcap_kernel(float* y, float cap, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        y[idx] = cap * tanhf(y[idx] / cap);
+}
+
+IL_EXPORT int il_softcap(float* y, float cap, long long total, cudaStream_t stream) {
+    if (total <= 0) return IL_OK;
+    if (!(cap > 0.f)) return IL_BAD_ARG;
+    softcap_kernel<<<sm_grid((size_t)total, 256), 256, 0, stream>>>(y, cap, (size_t)total);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

@@ -1,9 +1,16 @@
-// SwiGLU on a fused gate-up activation: out[t,i] = silu(gu[t,i]) * gu[t,I+i], computed in f32.
+// Gated activation on a fused gate-up product: out[t,i] = act(gu[t,i]) * gu[t,I+i], computed in f32; act: SiLU (SwiGLU) or
+// the tanh form of GELU.
 // Also a bias add for library matrix products that have no bias epilogue.
 #include "common.cuh"
 
 template <typename TA>
-__global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total) {
+__device__ __forceinline__ float gated(float g, float u, int act) {
+    if (act == IL_ACT_GELU_TANH) return sizeof(TA) == 2 ? il_gelu_tanh_mul_fast(g, u) : il_gelu_tanh_mul(g, u);
+    return sizeof(TA) == 2 ? il_silu_mul_fast(g, u) : g / (1.f + expf(-g)) * u;
+}
+
+template <typename TA>
+__global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total, int act) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -11,13 +18,13 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
         const int i = (int)(idx - t * I);
         const float g = il_to_f(gu[t * 2 * I + i]);
         const float u = il_to_f(gu[t * 2 * I + I + i]);
-        out[idx] = il_from_f<TA>(sizeof(TA) == 2 ? il_silu_mul_fast(g, u) : g / (1.f + expf(-g)) * u);
+        out[idx] = il_from_f<TA>(gated<TA>(g, u, act));
     }
 }
 
 // 8 bfloat16 (or 4 float) per thread and access; I must be a multiple of the vector width.
 template <typename TA, int VEC>
-__global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total_vec) {
+__global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total_vec, int act) {
     const int ivec = I / VEC;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -33,7 +40,7 @@ __global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ ou
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             const float g = il_to_f(gp[k]), u = il_to_f(up[k]);
-            op[k] = il_from_f<TA>(sizeof(TA) == 2 ? il_silu_mul_fast(g, u) : g / (1.f + expf(-g)) * u);
+            op[k] = il_from_f<TA>(gated<TA>(g, u, act));
         }
         *reinterpret_cast<uint4*>(out + t * I + i) = oq;
     }
@@ -55,15 +62,16 @@ static inline int grid_for(size_t total, int threads) {
     return (int)(g > cap ? cap : g);
 }
 
-IL_EXPORT int il_swiglu(const void* gu, void* out, int act_kind, int T, int I, cudaStream_t stream) {
+IL_EXPORT int il_swiglu(const void* gu, void* out, int act_kind, int T, int I, int act, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
+    if (act != IL_ACT_SILU && act != IL_ACT_GELU_TANH) return IL_BAD_ARG;
     if (I <= 0) return IL_BAD_ARG;
     const size_t total = (size_t)T * I;
     if (act_kind == IL_BF16 && I % 8 == 0) {
         const size_t tv = total / 8;
         size_t g = (tv + 255) / 256;
         if (g > 148 * 32) g = 148 * 32;
-        swiglu_vec_kernel<__nv_bfloat16, 8><<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, tv);
+        swiglu_vec_kernel<__nv_bfloat16, 8><<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, tv, act);
         IL_LAUNCH_CHECK();
         return IL_OK;
     }
@@ -71,15 +79,15 @@ IL_EXPORT int il_swiglu(const void* gu, void* out, int act_kind, int T, int I, c
         const size_t tv = total / 4;
         size_t g = (tv + 255) / 256;
         if (g > 148 * 32) g = 148 * 32;
-        swiglu_vec_kernel<float, 4><<<(int)g, 256, 0, stream>>>((const float*)gu, (float*)out, I, tv);
+        swiglu_vec_kernel<float, 4><<<(int)g, 256, 0, stream>>>((const float*)gu, (float*)out, I, tv, act);
         IL_LAUNCH_CHECK();
         return IL_OK;
     }
     const int threads = 256, grid = grid_for(total, threads);
     if (act_kind == IL_F32)
-        swiglu_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+        swiglu_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I, total, act);
     else if (act_kind == IL_BF16)
-        swiglu_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+        swiglu_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total, act);
     else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

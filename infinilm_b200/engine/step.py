@@ -139,6 +139,8 @@ class StepRunner:
         self.tokens_run = 0
         self.portion_replays = 0                  # steps with prompt portions that were replayed as graphs
         self._last_decode: Optional["_DecodeBatch"] = None    # the replayed decode step just run, if the next may follow it
+        # per cache owner (run-order entries, then the embedding): None for one need or none, else how many it has
+        self._needs_per_entry = [len(n) if isinstance(n, (tuple, list)) else None for n in model.cache_needs()]
         self.fast_steps = 0
 
     # -- descriptor buffers ----------------------------------------------------------------
@@ -424,17 +426,21 @@ class StepRunner:
         owners = [i if st.cache_from is None else st.cache_from for i, st in enumerate(self.model.order)]
         if self.model.embedding_cache_index is not None:      # what the embedding keeps of a request comes last
             owners.append(self.model.embedding_cache_index)
-        for i, owner in enumerate(owners):
+        def cache_view(owner, writable):
             g = self.cache.group_of_entry.get(owner)
             if g is None:
-                caches.append(None)
-                continue
+                return None
             grp = groups[g]
             if grp.need.kind == "paged_kv":
-                caches.append(PagedKVView(grp.storage[owner], view(s_bt[g]).view(Ep, widths[g]), kpage,
-                                          writable=(owner == i), max_pages=widths[g], tma_map=grp.tma_maps.get(owner)))
-            else:
-                caches.append(StateView(grp.storage[owner], view(s_rs), view(s_wsl), writable=(owner == i)))
+                return PagedKVView(grp.storage[owner], view(s_bt[g]).view(Ep, widths[g]), kpage,
+                                   writable=writable, max_pages=widths[g], tma_map=grp.tma_maps.get(owner))
+            return StateView(grp.storage[owner], view(s_rs), view(s_wsl), writable=writable)
+        for i, owner in enumerate(owners):
+            n_needs = self._needs_per_entry[owner]
+            if n_needs is None:                   # one need or none: one view or None
+                caches.append(cache_view(owner, owner == i))
+            else:                                 # a tuple of needs: a tuple of views, in the same order
+                caches.append(tuple(cache_view((owner, j), owner == i) for j in range(n_needs)))
 
         if graph_key is None:
             logits = self.model.forward(ctx, caches)

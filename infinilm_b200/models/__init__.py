@@ -5,7 +5,7 @@ import importlib
 
 from .causal_lm import CausalLM
 
-BUILTIN = ("minicpm4", "nirozen")
+BUILTIN = ("minicpm4", "nirozen", "gopitar")
 
 
 def register_builtin() -> None:

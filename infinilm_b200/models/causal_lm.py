@@ -37,10 +37,13 @@ class CausalLM:
                     raise ValueError(f"run order entry {i} adds row {st.add_row} of a table the model does not have")
                 if not self.blocks[st.layer].takes_pre_add:
                     raise ValueError(f"run order entry {i}: its block's arrangement cannot add a vector first")
+            if st.add_embedding and (st.add_row is not None or not self.blocks[st.layer].takes_pre_add):
+                raise ValueError(f"run order entry {i}: the embedding's output cannot be added before this block (or not beside a table row)")
             if not 0 <= st.layer < len(self.blocks):
                 raise ValueError(f"run order entry {i} names layer {st.layer}, which does not exist")
             if st.cache_from is not None and not (0 <= st.cache_from < i and self.order[st.cache_from].cache_from is None):
                 raise ValueError(f"run order entry {i}: cache_from must name an earlier entry that owns its cache")
+        self.keeps_embedding = any(st.add_embedding for st in self.order)
         self.hidden = self.embedding.hidden
         self.vocab = self.head.vocab
         # decode steps are replayed as CUDA graphs only if every part says it can be (`Part.graph_safe`)
@@ -61,7 +64,8 @@ class CausalLM:
 
     # -- cache -----------------------------------------------------------------------------
     def cache_needs(self) -> List[Optional[CacheNeed]]:
-        """One entry per run-order entry: what it keeps (None: nothing, or it reads another's); then one more for the
+        """One entry per run-order entry: what it keeps (None: nothing, or it reads another's; a `CacheNeed`; or a tuple of
+        them, for a mixer that keeps several things); then one more for the
         embedding, if that keeps something of a request between steps (`embedding_cache_index`)."""
         needs = []
         for st in self.order:
@@ -86,13 +90,19 @@ class CausalLM:
             self.embedding.forward(ctx.token_ids, resid, ctx, caches[ec] if ec is not None else None)
         else:
             self.embedding.forward(ctx.token_ids, resid)
+        emb_out = None
+        if self.keeps_embedding:                  # a later entry adds the embedding's output again: a second copy of it, float32
+            emb_out = ctx.ws.rows("embedding_out", T, self.hidden, torch.float32)
+            if getattr(self.embedding, "takes_context", False):
+                raise ValueError("an embedding that keeps state cannot be run twice in a step")
+            self.embedding.forward(ctx.token_ids, emb_out)
         pending = None
         for i, st in enumerate(self.order):
             # the block that runs next may take its first norm half done (its weights applied, the rms still to divide by)
             blk = self.blocks[st.layer]
             nxt_st = self.order[i + 1] if i + 1 < len(self.order) else None
-            nxt = self.blocks[nxt_st.layer] if nxt_st is not None and nxt_st.add_row is None else None
-            kw = {} if st.add_row is None else {"pre_add": self.pass_vectors.row(st.add_row)}
+            nxt = self.blocks[nxt_st.layer] if nxt_st is not None and nxt_st.add_row is None and not nxt_st.add_embedding else None
+            kw = {"pre_add": emb_out} if st.add_embedding else {} if st.add_row is None else {"pre_add": self.pass_vectors.row(st.add_row)}
             if blk.takes_next_norm and nxt is not None and nxt.accepts_normed_input(T):
                 pending = blk.run(resid, pending, ctx, caches[i], next_norm=nxt.mixer_norm, **kw)
             else:

@@ -127,13 +127,15 @@ def patch_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src_idx: torch.Ten
 
 def add_rmsnorm(resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scale: float, weight: torch.Tensor,
                 eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None, vec: Optional[torch.Tensor] = None) -> None:
-    """resid += branch_scale * branch (+ vec, one float32 vector for every row) (f32, in place); out = RMSNorm(resid) * weight.
+    """resid += branch_scale * branch (+ vec: float32, one [H] vector for every row or a [T,H] row for each) (f32, in place);
+    out = RMSNorm(resid) * weight.
 
     With `rows` (int32 indices) only those rows are normalised, into out[0..len(rows)), and
     `resid` is left as it was."""
     _need_cuda(resid, branch, weight, out, rows, vec)
-    if vec is not None and (vec.dtype != torch.float32 or vec.numel() != resid.shape[1] or not vec.is_contiguous()):
-        raise KernelError("add_rmsnorm: vec must be a contiguous float32 [H]")
+    if vec is not None and (vec.dtype != torch.float32 or not vec.is_contiguous()
+                            or (vec.numel() != resid.shape[1] and tuple(vec.shape) != tuple(resid.shape))):
+        raise KernelError("add_rmsnorm: vec must be a contiguous float32 [H] or [T,H]")
     T, H = resid.shape
     n = T if rows is None else rows.numel()
     if resid.dtype != torch.float32 or weight.numel() != H or out.shape[-1] != H or out.shape[0] < n:
@@ -146,20 +148,23 @@ def add_rmsnorm(resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scal
     if branch is not None:
         _contig("branch", branch)
     f = _fn("rmsnorm", "il_add_rmsnorm", [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_float, _c_void_p,
-                                          _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p])
+                                          _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p])
     _check(f(_ptr(resid), _ptr(branch), branch_scale, _ptr(weight), kind_of(weight.dtype), eps, _ptr(out),
-             kind_of(out.dtype), _ptr(rows), n, H, _ptr(vec), _stream()), "add_rmsnorm")
+             kind_of(out.dtype), _ptr(rows), n, H, _ptr(vec), H if vec is not None and vec.dim() == 2 else 0, _stream()), "add_rmsnorm")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i]."""
+ACT_SILU, ACT_GELU_TANH = 1, 2                    # the gate of a gated feed-forward
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, act: int = ACT_SILU) -> None:
+    """out[t,i] = act(gate_up[t,i]) * gate_up[t,I+i]; act: SiLU or the tanh form of GELU."""
     _need_cuda(gate_up, out)
     T, I2 = gate_up.shape
     if I2 % 2 or out.shape != (T, I2 // 2) or out.dtype != gate_up.dtype:
         raise KernelError("swiglu: gate_up [T,2I], out [T,I] of the same dtype")
     _contig("gate_up", gate_up), _contig("out", out)
-    f = _fn("swiglu", "il_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
-    _check(f(_ptr(gate_up), _ptr(out), kind_of(out.dtype), T, I2 // 2, _stream()), "swiglu")
+    f = _fn("swiglu", "il_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), kind_of(out.dtype), T, I2 // 2, act, _stream()), "swiglu")
 
 
 def add_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
@@ -453,9 +458,9 @@ def _norm_args(norm_in: Optional[NormedInput], M: int):
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
-                bias: Optional[torch.Tensor] = None, glu: bool = False, norm_in: Optional[NormedInput] = None) -> None:
+                bias: Optional[torch.Tensor] = None, glu: int = 0, norm_in: Optional[NormedInput] = None) -> None:
     """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) for M <= 16 bfloat16 rows; out bfloat16 or float32.
-    glu: w is [2N,K] (gate rows, then up rows) and out[M,N] = silu(gate) * up.
+    glu (True, or ACT_SILU / ACT_GELU_TANH): w is [2N,K] (gate rows, then up rows) and out[M,N] = act(gate) * up.
     norm_in (with glu, or with a bfloat16 out): x is `norm_in.xw`, and the results are divided by the rms that its sums give."""
     _need_cuda(x, w, out, bias)
     M, K = x.shape
@@ -623,10 +628,10 @@ def mid_ok(M: int, K: int) -> bool:
 
 
 def gemm_mid(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0, bias: Optional[torch.Tensor] = None,
-             glu: bool = False, nb: int = 0, bm: int = 0) -> None:
+             glu: int = 0, nb: int = 0, bm: int = 0) -> None:
     """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) for 17..128 bfloat16 rows on the tcgen05 tensor cores: tiles of 64
     or 128 weight rows (`bm`; the A operand) by blocks of `nb` activation rows (0: chosen by the kernel) over all of K; out bfloat16
-    or float32. glu: w is [2N,K] (gate rows, then up rows) and out[M,N] = silu(gate) * up (bfloat16)."""
+    or float32. glu (True, or ACT_SILU / ACT_GELU_TANH): w is [2N,K] (gate rows, then up rows) and out[M,N] = act(gate) * up (bfloat16)."""
     _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0] // 2 if glu else w.shape[0]
@@ -958,3 +963,155 @@ def step_fill(out, out_cap: int, E: int, Ep: int, Tp: int, order, n_tok, start, 
                  _np_ptr(scratch_page), scratch_slot, _np_ptr(want), _np_ptr(want_off), int(pad_at), int(n_want_fixed), n_patch_cap,
                  _c_void_p(offsets.ctypes.data), _c_void_p(outs.ctypes.data), _c_void_p(outs.ctypes.data + 4),
                  _c_void_p(outs.ctypes.data + 8)))
+
+
+# ---- sequence mixers with a state of fixed size (csrc/seqmix.cu) ---------------------------------------------------------
+def _i32(name: str, *ts: torch.Tensor) -> None:
+    for t in ts:
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"{name}: descriptors must be contiguous int32 tensors")
+
+
+def short_conv(x: torch.Tensor, x_off: int, w: torch.Tensor, state: torch.Tensor, st_off: int, read_slots: torch.Tensor,
+               tok_entry: torch.Tensor, entry_qstart: torch.Tensor, out: torch.Tensor, out_off: int, n_seg: int, seg_in: int,
+               seg_out: int, act: int = 0) -> None:
+    """Causal convolution over time of n_seg * seg_in channels of `x` (columns from x_off), per channel, with weights
+    w float32 [channels, taps] whose last column meets the current token. Inputs before a step's first row come from
+    `state` (float32 [slots, taps-1, all channels], this call's channels from column st_off; slot read_slots[entry]).
+    Written to `out` from column out_off as n_seg segments of seg_out >= seg_in columns, the surplus zero. act 1: silu."""
+    _need_cuda(x, w, state, read_slots, tok_entry, entry_qstart, out)
+    _i32("short_conv", read_slots, tok_entry, entry_qstart)
+    T, taps = x.shape[0], w.shape[1]
+    if w.dtype != torch.float32 or not w.is_contiguous() or w.shape[0] != n_seg * seg_in:
+        raise KernelError("short_conv: w float32 [channels, taps]")
+    if state.dtype != torch.float32 or not state.is_contiguous() or state.dim() != 3 or state.shape[1] != max(taps - 1, 1):
+        raise KernelError("short_conv: state float32 [slots, taps-1, channels]")
+    if (x.stride(1) != 1 or out.stride(1) != 1 or out.shape[0] != T or x_off + n_seg * seg_in > x.shape[1]
+            or out_off + n_seg * seg_out > out.shape[1] or st_off + n_seg * seg_in > state.shape[2]):
+        raise KernelError("short_conv: column ranges do not fit")
+    f = _fn("seqmix", "il_short_conv", [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_ll, _c_int, _c_int,
+                                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                        _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), x_off, _ptr(w), taps, _ptr(state), state.stride(0), st_off, state.shape[2],
+             _ptr(read_slots), _ptr(tok_entry), _ptr(entry_qstart), _ptr(out), kind_of(out.dtype), out.stride(0), out_off, n_seg,
+             seg_in, seg_out, act, T, _stream()), "short_conv")
+
+
+def short_conv_state(x: torch.Tensor, x_off: int, n_channels: int, taps: int, state: torch.Tensor, st_off: int,
+                     read_slots: torch.Tensor, write_slots: torch.Tensor, entry_qstart: torch.Tensor, n_entries: int) -> None:
+    """The convolution's state after the step: the last taps-1 inputs of every entry, into slot write_slots[entry]."""
+    if taps <= 1:
+        return
+    _need_cuda(x, state, read_slots, write_slots, entry_qstart)
+    _i32("short_conv_state", read_slots, write_slots, entry_qstart)
+    if state.dtype != torch.float32 or not state.is_contiguous() or state.dim() != 3 or state.shape[1] != taps - 1:
+        raise KernelError("short_conv_state: state float32 [slots, taps-1, channels]")
+    if x.stride(1) != 1 or x_off + n_channels > x.shape[1] or st_off + n_channels > state.shape[2]:
+        raise KernelError("short_conv_state: column ranges do not fit")
+    f = _fn("seqmix", "il_short_conv_state", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_ll, _c_int, _c_int,
+                                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p])
+    _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), x_off, n_channels, taps, _ptr(state), state.stride(0), st_off, state.shape[2],
+             _ptr(read_slots), _ptr(write_slots), _ptr(entry_qstart), n_entries, _stream()), "short_conv_state")
+
+
+def delta_prep(qk: torch.Tensor, q_off: int, k_off: int, n_qk_heads: int, dim: int, q_scale: float, unit_eps: float,
+               ab: torch.Tensor, b_off: int, a_off: int, a_log: torch.Tensor, dt_bias: torch.Tensor, beta: torch.Tensor,
+               gdec: torch.Tensor, n_heads: int) -> None:
+    """In place: the q and k heads of `qk` (float32) become unit vectors, x / sqrt(sum x^2 + unit_eps), q also times q_scale.
+    beta[t,h] = sigmoid(ab[t, b_off+h]); gdec[t,h] = exp(-exp(a_log[h]) * softplus(ab[t, a_off+h] + dt_bias[h]))."""
+    _need_cuda(qk, ab, a_log, dt_bias, beta, gdec)
+    T = qk.shape[0]
+    for t in (qk, ab, a_log, dt_bias, beta, gdec):
+        if t.dtype != torch.float32:
+            raise KernelError("delta_prep: float32 tensors")
+    if (qk.stride(1) != 1 or ab.stride(1) != 1 or a_log.numel() != n_heads or dt_bias.numel() != n_heads
+            or tuple(beta.shape) != (T, n_heads) or tuple(gdec.shape) != (T, n_heads) or not beta.is_contiguous() or not gdec.is_contiguous()):
+        raise KernelError("delta_prep: shapes")
+    f = _fn("seqmix", "il_delta_prep", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_int, _c_int,
+                                        _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(qk), qk.stride(0), q_off, k_off, n_qk_heads, dim, q_scale, unit_eps, _ptr(ab), ab.stride(0), b_off, a_off,
+             _ptr(a_log), _ptr(dt_bias), _ptr(beta), _ptr(gdec), n_heads, T, _stream()), "delta_prep")
+
+
+SCAN_DECAY, SCAN_DELTA = 0, 1
+
+
+def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n_qk_heads: int, dim: int,
+                      vdim: int, in_act: int, decay: Optional[torch.Tensor], beta: Optional[torch.Tensor],
+                      gdec: Optional[torch.Tensor], state: torch.Tensor, read_slots: torch.Tensor, write_slots: torch.Tensor,
+                      entry_qstart: torch.Tensor, n_entries: int, out: torch.Tensor) -> None:
+    """A recurrence over a float32 state S [dim, vdim] per (request, head), token by token in each entry's order.
+    SCAN_DECAY: S = decay[h] S + k v^T, o = S^T q. SCAN_DELTA: S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q.
+    q, k float32 [T, >= n_qk_heads*dim] (views with a row stride), v float32 [T, >= n_heads*vdim], out float32 [T, n_heads*vdim];
+    value head h reads q/k head h // (n_heads // n_qk_heads). in_act 1: silu on q, k, v as read.
+    state float32 [slots, n_heads, dim, vdim]."""
+    _need_cuda(q, k, v, decay, beta, gdec, state, read_slots, write_slots, entry_qstart, out)
+    _i32("matrix_state_scan", read_slots, write_slots, entry_qstart)
+    for t in (q, k, v, out, state):
+        if t.dtype != torch.float32 or t.stride(-1) != 1:
+            raise KernelError("matrix_state_scan: float32 tensors with contiguous rows")
+    if not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, vdim):
+        raise KernelError("matrix_state_scan: state float32 [slots, heads, dim, vdim]")
+    if out.shape[1] != n_heads * vdim or q.shape[1] < n_qk_heads * dim or k.shape[1] < n_qk_heads * dim or v.shape[1] < n_heads * vdim:
+        raise KernelError("matrix_state_scan: shapes")
+    f = _fn("seqmix", "il_matrix_state_scan", [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                               _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p,
+                                               _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p])
+    _check(f(mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), n_heads, n_qk_heads, dim, vdim, in_act,
+             _ptr(decay), _ptr(beta), _ptr(gdec), _ptr(state), state.stride(0), _ptr(read_slots), _ptr(write_slots),
+             _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), _stream()), "matrix_state_scan")
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def group_norm_gate(x: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor, g_off: int, act: int, out: torch.Tensor,
+                    group: int) -> None:
+    """out[t,j] = x[t,j] / sqrt(mean of x^2 over j's group of `group` columns + eps) * w[j % len(w)] * act(gate[t, g_off+j]);
+    x float32 [T,n], gate float32 or bfloat16 (a view with a row stride), out float32 or bfloat16 [T,n]."""
+    _need_cuda(x, w, gate, out)
+    T, n = x.shape
+    if x.dtype != torch.float32 or x.stride(1) != 1 or out.stride(1) != 1 or gate.stride(1) != 1 or tuple(out.shape) != (T, n):
+        raise KernelError("group_norm_gate: x float32 [T,n], out [T,n]")
+    if n % group or g_off + n > gate.shape[1] or not w.is_contiguous():
+        raise KernelError("group_norm_gate: groups must divide the row, the gate must cover it")
+    f = _fn("seqmix", "il_group_norm_gate", [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+                                             _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), kind_of(w.dtype), w.numel(), eps, _ptr(gate), kind_of(gate.dtype), gate.stride(0), g_off,
+             act, _ptr(out), kind_of(out.dtype), out.stride(0), group, n // group, T, _stream()), "group_norm_gate")
+
+
+def head_gate(y: torch.Tensor, head_dim: int, gate: Optional[torch.Tensor], g_off: int, out: torch.Tensor, n_heads: int, vdim: int) -> None:
+    """out[t, h*vdim + c] = y[t, h*head_dim + c] * sigmoid(gate[t, g_off + h]) for c < vdim: one gate per head, and heads that
+    were padded to head_dim columns come out packed (`gate` None: only that)."""
+    _need_cuda(y, gate, out)
+    T = y.shape[0]
+    if y.dtype != out.dtype or y.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("head_gate: one dtype, contiguous rows")
+    if gate is not None and (gate.dtype != y.dtype or gate.stride(1) != 1 or g_off + n_heads > gate.shape[1]):
+        raise KernelError("head_gate: the gate has y's dtype and one column per head")
+    if y.shape[1] != n_heads * head_dim or tuple(out.shape) != (T, n_heads * vdim):
+        raise KernelError("head_gate: shapes")
+    f = _fn("seqmix", "il_head_gate", [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int,
+                                       _c_int, _c_void_p])
+    _check(f(_ptr(y), kind_of(y.dtype), y.stride(0), head_dim, _ptr(gate), 0 if gate is None else gate.stride(0), g_off, _ptr(out),
+             out.stride(0), n_heads, vdim, T, _stream()), "head_gate")
+
+
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float, out: torch.Tensor) -> None:
+    """out = sa * a + sb * b, summed in float32; three contiguous tensors of one shape and dtype (out may be a or b)."""
+    _need_cuda(a, b, out)
+    if a.shape != b.shape or a.shape != out.shape or a.dtype != b.dtype or a.dtype != out.dtype:
+        raise KernelError("scaled_sum: one shape and dtype")
+    _contig("a", a), _contig("b", b), _contig("out", out)
+    f = _fn("seqmix", "il_scaled_sum", [_c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_int, _c_ll, _c_void_p])
+    _check(f(_ptr(a), sa, _ptr(b), sb, _ptr(out), kind_of(out.dtype), out.numel(), _stream()), "scaled_sum")
+
+
+def softcap(y: torch.Tensor, cap: float) -> None:
+    """y = cap * tanh(y / cap) in place, float32."""
+    _need_cuda(y)
+    if y.dtype != torch.float32 or not y.is_contiguous():
+        raise KernelError("softcap: contiguous float32")
+    f = _fn("seqmix", "il_softcap", [_c_void_p, _c_float, _c_ll, _c_void_p])
+    _check(f(_ptr(y), cap, y.numel(), _stream()), "softcap")

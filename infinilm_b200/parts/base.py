@@ -87,7 +87,9 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_need(self) -> Optional[CacheNeed]:
+    def cache_need(self):
+        """None, one `CacheNeed`, or a tuple of them (pages and a state, two states): `forward` then gets None, one cache
+        view, or a tuple of views in the same order."""
         return None
 
     # A part that can read an `ops.NormedInput` as `x`, or take a `tail=ResidualTail` in `forward` and return the
@@ -179,4 +181,5 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from . import attention, blocks, embedding, feed_forward, latent_attention, moe, norms, position  # noqa: F401
+        from . import (attention, blocks, conv_attention, embedding, feed_forward, latent_attention, linear_recurrence, moe, norms,  # noqa: F401
+                       parallel, position)

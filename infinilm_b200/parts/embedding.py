@@ -20,28 +20,31 @@ from .spec import WeightSpec
 
 
 class TokenEmbedding(Part):
-    """params: vocab, hidden, scale."""
+    """params: vocab, hidden, scale; name (local tensor name, default "weight"); exact (default False: on the bfloat16 path
+    row x scale is rounded through bfloat16, the value a table scaled at load would hold; True: the float32 product enters
+    the residual stream as it is)."""
     graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
         self.vocab, self.hidden, self.scale = int(params["vocab"]), int(params["hidden"]), float(params.get("scale", 1.0))
+        self.name, self.exact = str(params.get("name", "weight")), bool(params.get("exact", False))
         self.table: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec("weight", (self.vocab, self.hidden))]
+        return [WeightSpec(self.name, (self.vocab, self.hidden))]
 
     def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
-        self.table = t["weight"].to(self.dtype).contiguous()
+        self.table = t[self.name].to(self.dtype).contiguous()
 
     def forward(self, token_ids: torch.Tensor, resid: torch.Tensor) -> torch.Tensor:
-        ops.embed(token_ids, self.table, self.scale, resid, round_bf16=(self.dtype == torch.bfloat16))
+        ops.embed(token_ids, self.table, self.scale, resid, round_bf16=(self.dtype == torch.bfloat16 and not self.exact))
         return resid
 
 
 class OutputHead(Part):
     """params: vocab, hidden, scale, tied_to (full name of the embedding table or None), name (local tensor name,
-    default "weight"). Logits are float32 on both paths."""
+    default "weight"), softcap (None, or c: logits = c * tanh(logits / c)). Logits are float32 on both paths."""
     graph_safe = True
 
     def __init__(self, params, prefix, dtype):
@@ -50,6 +53,9 @@ class OutputHead(Part):
         self.linear = Linear(self.hidden, self.vocab, dtype, alpha=float(params.get("scale", 1.0)), use_tc5=True)
         self.tied_to = params.get("tied_to")
         self.name = str(params.get("name", "weight"))
+        self.softcap = None if params.get("softcap") is None else float(params["softcap"])
+        if self.softcap is not None and not self.softcap > 0.0:
+            raise ValueError("output head: the soft cap must be positive")
 
     def weight_specs(self) -> List[WeightSpec]:
         return [WeightSpec(self.name, (self.vocab, self.hidden), fallback=self.tied_to)]
@@ -58,7 +64,10 @@ class OutputHead(Part):
         self.linear.set(t[self.name])
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        return self.linear(x, out, out_f32=True)
+        self.linear(x, out, out_f32=True)
+        if self.softcap is not None:
+            ops.softcap(out, self.softcap)
+        return out
 
 
 class PairPositionEmbedding(Part):

@@ -1,4 +1,4 @@
-"""Dense SwiGLU feed-forward: down(silu(gate(x)) * up(x)).
+"""Dense gated feed-forward: down(act(gate(x)) * up(x)), act SiLU (SwiGLU) or the tanh form of GELU.
 
 Parity with InfiniLM: `csrc/layers/mlp/mlp.cpp:7-38` (gate and up as one product, `swiglu(up, gate)`,
 then down), `csrc/layers/linear/fused_linear.cpp:152-158,177-185` (gate rows first, up rows second).
@@ -16,29 +16,40 @@ from .spec import WeightSpec
 
 
 class SwiGLU(FeedForward):
-    """params: hidden, intermediate, bias, out_scale."""
+    """params: hidden, intermediate, bias, out_scale; activation ("silu", the default, or "gelu_tanh": the gate's function);
+    names (local tensor names of the three weights, default gate_proj.weight / up_proj.weight / down_proj.weight)."""
     graph_safe = True
+    ACTIVATIONS = {"silu": ops.ACT_SILU, "gelu_tanh": ops.ACT_GELU_TANH}
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
         self.hidden, self.inter = int(params["hidden"]), int(params["intermediate"])
         self.bias = bool(params.get("bias", False))
+        act = str(params.get("activation", "silu"))
+        if act not in self.ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: activation {act!r} is not one of {', '.join(self.ACTIVATIONS)}")
+        self.act = self.ACTIVATIONS[act]
+        names = params.get("names") or {}
+        self.n_gate, self.n_up, self.n_down = (str(names.get(k, d)) for k, d in
+                                               (("gate", "gate_proj.weight"), ("up", "up_proj.weight"), ("down", "down_proj.weight")))
+        if self.bias and names:
+            raise ValueError("gated feed-forward: biases go with the default tensor names")
         self.gate_up = Linear(self.hidden, 2 * self.inter, dtype)
         self.down = Linear(self.inter, self.hidden, dtype, alpha=float(params.get("out_scale", 1.0)))
 
     def weight_specs(self) -> List[WeightSpec]:
-        specs = [WeightSpec("gate_proj.weight", (self.inter, self.hidden)), WeightSpec("up_proj.weight", (self.inter, self.hidden)),
-                 WeightSpec("down_proj.weight", (self.hidden, self.inter))]
+        specs = [WeightSpec(self.n_gate, (self.inter, self.hidden)), WeightSpec(self.n_up, (self.inter, self.hidden)),
+                 WeightSpec(self.n_down, (self.hidden, self.inter))]
         if self.bias:
             specs += [WeightSpec("gate_proj.bias", (self.inter,), "vector"), WeightSpec("up_proj.bias", (self.inter,), "vector"),
                       WeightSpec("down_proj.bias", (self.hidden,), "vector")]
         return specs
 
     def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
-        w = torch.cat([t["gate_proj.weight"], t["up_proj.weight"]], dim=0)
+        w = torch.cat([t[self.n_gate], t[self.n_up]], dim=0)
         b = torch.cat([t["gate_proj.bias"].float(), t["up_proj.bias"].float()]) if self.bias else None
         self.gate_up.set(w, b)
-        self.down.set(t["down_proj.weight"], t.get("down_proj.bias"))
+        self.down.set(t[self.n_down], t.get("down_proj.bias"))
 
     def accepts_normed(self, T):
         return self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden)
@@ -52,9 +63,9 @@ class SwiGLU(FeedForward):
             # decode: gate and up rows streamed together, SiLU(gate)*up in the epilogue
             act = ctx.ws.rows("ffn_act", T, self.inter, self.dtype)
             if isinstance(x, ops.NormedInput):
-                ops.gemm_skinny(x.xw, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True, norm_in=x)
+                ops.gemm_skinny(x.xw, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=self.act, norm_in=x)
             else:
-                ops.gemm_skinny(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True)
+                ops.gemm_skinny(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=self.act)
             if tail is not None:                  # down adds into the residual and prepares the next norm itself
                 return ops.gemm_skinny_resid(act, self.down.weight, self.down.alpha, self.down.bias, tail.resid, tail.scale,
                                              tail.norm.weight, tail.norm.eps,
@@ -66,10 +77,10 @@ class SwiGLU(FeedForward):
             # 17..128 rows: gate and up on the tcgen05 tensor cores as two accumulators in the same lanes, SiLU(gate)*up in
             # the epilogue (measured against the library product followed by the SwiGLU kernel at 8B sizes: 44.6 against
             # 48.4 us at 32 rows, 47.6 against 49.9 at 64, 52.5 against 57.6 at 128)
-            ops.gemm_mid(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True)
+            ops.gemm_mid(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=self.act)
             return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
         gu = self.gate_up(x, ctx.ws.rows("gate_up", T, 2 * self.inter, self.dtype))
-        ops.swiglu(gu, act)
+        ops.swiglu(gu, act, self.act)
         return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
 
 

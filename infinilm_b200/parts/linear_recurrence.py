@@ -1,0 +1,141 @@
+"""Mixers that keep a matrix per head instead of keys: a decayed sum of outer products ("lightning" linear attention)
+and the gated delta rule. Both run their recurrence token by token in float32, from a float32 state per request.
+
+DecayLinearAttention:
+    q = silu(W_q h), k = silu(W_k h), v = silu(W_v h);  per head  S_t = decay_h S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t
+    y = W_o ( rms_norm(o over all heads) * w * sigmoid(W_g h) )
+GatedDeltaRule:
+    q, k, v = silu(short_conv(W_q h)), silu(short_conv(W_k h)), silu(short_conv(W_v h));  q, k unit vectors per head, q / sqrt(dim)
+    beta = sigmoid(W_b h),  g = exp(-exp(A_log) softplus(W_a h + dt_bias))
+    per head  S = g S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q      (the read-out sees the token's own write)
+    y = W_o ( rms_norm(o per head) * w * silu(W_g h) )
+The projections leave float32 on both paths (what enters a recurrence, its gates and decays stay 32-bit).
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import ops
+from .base import Mixer, register_part
+from .linear import Linear
+from .short_conv import ShortConv
+from .spec import CacheNeed, WeightSpec
+
+
+class DecayLinearAttention(Mixer):
+    """params: hidden, n_heads, qk_dim, v_dim, decay (one number per head), eps (of the output norm).
+    Tensors: q, k, v, g, o [out, in]; norm [heads * v_dim]."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        p = params
+        self.hidden, self.nh, self.dk, self.dv = int(p["hidden"]), int(p["n_heads"]), int(p["qk_dim"]), int(p["v_dim"])
+        self.eps = float(p["eps"])
+        self.decay_list = [float(x) for x in p["decay"]]
+        if len(self.decay_list) != self.nh:
+            raise ValueError(f"linear attention: {len(self.decay_list)} decays for {self.nh} heads")
+        self.nqk, self.nv = self.nh * self.dk, self.nh * self.dv
+        self.proj = Linear(self.hidden, 2 * self.nqk + 2 * self.nv, dtype)          # [q | k | v | g]
+        self.o_proj = Linear(self.nv, self.hidden, dtype)
+        self.decay = self.norm_w = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        H = self.hidden
+        return [WeightSpec("q", (self.nqk, H)), WeightSpec("k", (self.nqk, H)), WeightSpec("v", (self.nv, H)), WeightSpec("g", (self.nv, H)),
+                WeightSpec("o", (H, self.nv)), WeightSpec("norm", (self.nv,), "vector", ("ones_normal", 0.05))]
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        self.proj.set(torch.cat([t["q"], t["k"], t["v"], t["g"]], dim=0))
+        self.o_proj.set(t["o"])
+        self.norm_w = t["norm"].contiguous()
+        self.decay = torch.tensor(self.decay_list, dtype=torch.float64).to(torch.float32).to(t["q"].device)
+
+    def cache_need(self):
+        return CacheNeed("state", shape=(self.nh, self.dk, self.dv), dtype="float32")
+
+    def forward(self, x, ctx, cache):
+        T, nqk, nv = x.shape[0], self.nqk, self.nv
+        proj = self.proj(x, ctx.ws.rows("dla_proj", T, 2 * nqk + 2 * nv, torch.float32), out_f32=True)
+        o = ctx.ws.rows("dla_o", T, nv, torch.float32)
+        ops.matrix_state_scan(ops.SCAN_DECAY, proj[:, :nqk], proj[:, nqk: 2 * nqk], proj[:, 2 * nqk: 2 * nqk + nv], self.nh, self.nh,
+                              self.dk, self.dv, 1, self.decay, None, None, cache.storage, cache.read_slots,
+                              cache.write_slots if cache.writable else cache.read_slots, ctx.entry_qstart, ctx.n_entries, o)
+        gated = ctx.ws.rows("dla_gated", T, nv, self.dtype)
+        ops.group_norm_gate(o, self.norm_w, self.eps, proj, 2 * nqk + nv, ops.GATE_SIGMOID, gated, nv)
+        return self.o_proj(gated, ctx.ws.rows("dla_branch", T, self.hidden, self.dtype))
+
+
+class GatedDeltaRule(Mixer):
+    """params: hidden, n_heads (value heads), n_qk_heads, qk_dim, v_dim, conv_taps, eps (of the output norm), unit_eps (inside
+    the root that makes q and k unit vectors, default 1e-6).
+    Tensors: q, k [n_qk_heads * qk_dim, in], v, g [n_heads * v_dim, in], b, a [n_heads, in], o; q.conv, k.conv, v.conv
+    [channels, taps]; A_log, dt_bias [n_heads]; norm [v_dim]."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        p = params
+        self.hidden, self.nh, self.ng = int(p["hidden"]), int(p["n_heads"]), int(p["n_qk_heads"])
+        self.dk, self.dv, self.taps = int(p["qk_dim"]), int(p["v_dim"]), int(p.get("conv_taps") or 1)
+        if self.nh <= 0 or self.ng <= 0 or self.nh % self.ng:
+            raise ValueError(f"delta rule: {self.nh} value heads are not a multiple of {self.ng} q/k heads")
+        self.eps, self.unit_eps = float(p["eps"]), float(p.get("unit_eps", 1e-6))
+        self.nqk, self.nv = self.ng * self.dk, self.nh * self.dv
+        self.n_conv = 2 * self.nqk + self.nv
+        self.n_proj = self.n_conv + 2 * self.nh + self.nv                          # [q | k | v | b | a | g]
+        self.n_proj_pad = (self.n_proj + 7) // 8 * 8
+        self.proj = Linear(self.hidden, self.n_proj_pad, dtype)
+        self.o_proj = Linear(self.nv, self.hidden, dtype)
+        self.conv = ShortConv(self.n_conv, self.taps)
+        self.a_log = self.dt_bias = self.norm_w = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        H = self.hidden
+        specs = [WeightSpec("q", (self.nqk, H)), WeightSpec("k", (self.nqk, H)), WeightSpec("v", (self.nv, H)),
+                 WeightSpec("b", (self.nh, H)), WeightSpec("a", (self.nh, H)), WeightSpec("g", (self.nv, H)), WeightSpec("o", (H, self.nv)),
+                 WeightSpec("A_log", (self.nh,), "vector", ("normal", 0.5)), WeightSpec("dt_bias", (self.nh,), "vector", ("normal", 0.5)),
+                 WeightSpec("norm", (self.dv,), "vector", ("ones_normal", 0.05))]
+        if self.taps > 1:
+            specs += [WeightSpec(n + ".conv", (c, self.taps), "vector", ("normal", 0.5)) for n, c in (("q", self.nqk), ("k", self.nqk), ("v", self.nv))]
+        return specs
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        ws = [t["q"], t["k"], t["v"], t["b"], t["a"], t["g"]]
+        if self.n_proj_pad != self.n_proj:
+            ws.append(torch.zeros((self.n_proj_pad - self.n_proj, self.hidden), dtype=ws[0].dtype, device=ws[0].device))
+        self.proj.set(torch.cat(ws, dim=0))
+        self.o_proj.set(t["o"])
+        if self.taps > 1:
+            self.conv.set([t["q.conv"], t["k.conv"], t["v.conv"]])
+        else:
+            self.conv.set([torch.ones((self.n_conv, 1), dtype=torch.float32, device=t["q"].device)])
+        self.a_log, self.dt_bias = t["A_log"].to(torch.float32).contiguous(), t["dt_bias"].to(torch.float32).contiguous()
+        self.norm_w = t["norm"].contiguous()
+
+    def cache_need(self):
+        return (CacheNeed("state", shape=(self.nh, self.dk, self.dv), dtype="float32"), self.conv.state_need())
+
+    def forward(self, x, ctx, cache):
+        S, conv_state = cache
+        T, nqk, nv, nh = x.shape[0], self.nqk, self.nv, self.nh
+        proj = self.proj(x, ctx.ws.rows("gdr_proj", T, self.n_proj_pad, torch.float32), out_f32=True)
+        qkv = ctx.ws.rows("gdr_qkv", T, self.n_conv, torch.float32)
+        self.conv.run(proj, 0, ctx, conv_state, qkv, [(0, 1, self.n_conv, 0, self.n_conv)], act=1)
+        beta = ctx.ws.rows("gdr_beta", T, nh, torch.float32)
+        gdec = ctx.ws.rows("gdr_decay", T, nh, torch.float32)
+        ops.delta_prep(qkv, 0, nqk, self.ng, self.dk, self.dk ** -0.5, self.unit_eps, proj, self.n_conv, self.n_conv + nh,
+                       self.a_log, self.dt_bias, beta, gdec, nh)
+        o = ctx.ws.rows("gdr_o", T, nv, torch.float32)
+        ops.matrix_state_scan(ops.SCAN_DELTA, qkv[:, :nqk], qkv[:, nqk: 2 * nqk], qkv[:, 2 * nqk:], nh, self.ng, self.dk, self.dv, 0,
+                              None, beta, gdec, S.storage, S.read_slots, S.write_slots if S.writable else S.read_slots,
+                              ctx.entry_qstart, ctx.n_entries, o)
+        gated = ctx.ws.rows("gdr_gated", T, nv, self.dtype)
+        ops.group_norm_gate(o, self.norm_w, self.eps, proj, self.n_conv + 2 * nh, ops.GATE_SILU, gated, self.dv)
+        return self.o_proj(gated, ctx.ws.rows("gdr_branch", T, self.hidden, self.dtype))
+
+
+register_part("mixer", "decay_linear_attention", DecayLinearAttention)
+register_part("mixer", "gated_delta_rule", GatedDeltaRule)

@@ -35,10 +35,13 @@ class RunStep:
 
     `cache_from` names an earlier entry of the order whose cache this entry reads instead of
     keeping its own (it then writes nothing). `add_row`: row of the model's `pass_vectors` table that is added to the
-    residual stream right before this entry runs (a model that runs some layers several times marks each pass so)."""
+    residual stream right before this entry runs (a model that runs some layers several times marks each pass so).
+    `add_embedding`: the embedding's output - every token's row as it entered the first entry - is added to the residual
+    stream right before this entry runs (a model that feeds its input in again at the start of a later pass)."""
     layer: int
     cache_from: Optional[int] = None
     add_row: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass
@@ -72,7 +75,9 @@ class CacheNeed:
 
     kind "paged_kv": keys and values in pages; `window` None keeps all keys, else only the last
     `window` positions are ever read, so pages behind the window are given back.
-    kind "state": one fixed-size tensor of `shape` per request (slot 0 of the pool is the zero state)."""
+    kind "state": one fixed-size tensor of `shape` per request (slot 0 of the pool is the zero state).
+    A mixer that keeps several things (pages and a state, two states) returns a tuple of needs from `cache_need()` and gets
+    a tuple of views, in the same order."""
     kind: str
     n_kv_heads: int = 0
     head_dim: int = 0
