@@ -37,7 +37,7 @@ def _obj(raw: Dict[str, Any], key: str, required: bool = True) -> Optional[Dict[
 
 def _softmax_branch(m: Dict[str, Any]) -> Dict[str, Any]:
     out = {k: take(m, k, int) for k in ("heads", "kv_heads", "dim", "vdim")}
-    out["conv"] = take(m, "conv", int, 1)
+    out["conv"] = take(m, "conv", int, None)
     out["scale"] = take(m, "scale", float)
     mask, rot = _obj(m, "mask", required=False), _obj(m, "rot", required=False)
     out["window"] = None if mask is None else take(mask, "size", int)
@@ -82,7 +82,7 @@ class GopitarConfig(ModelConfig):
                          "left_scale": take(m, "left_scale", float, 1.0), "right_scale": take(m, "right_scale", float, 1.0)}
             else:
                 mixer = {k: take(m, k, int) for k in ("heads", "kv_heads", "dim", "vdim")}
-                mixer["conv"] = take(m, "conv", int, 1)
+                mixer["conv"] = take(m, "conv", int, None)
             mlp = None
             f = _obj(L, "mlp", required=False)
             if f is not None:

@@ -25,7 +25,7 @@ from .spec import CacheNeed, PartSpec, WeightSpec
 
 
 class ConvGatedAttention(Mixer):
-    """params: hidden, n_heads, n_kv_heads, qk_dim, v_dim, scale, window (None: all keys), conv_taps (None or 1: no
+    """params: hidden, n_heads, n_kv_heads, qk_dim, v_dim, scale, window (None: all keys), conv_taps (None: no
     convolution), qkv_bias, out_bias, head_gate, position (PartSpec of a rotary encoding, or None)."""
     graph_safe = True
 
@@ -43,7 +43,7 @@ class ConvGatedAttention(Mixer):
         self.window: Optional[int] = None if p.get("window") is None else int(p["window"])
         if self.window is not None and self.window < 1:
             raise ValueError("attention: a window holds at least the token itself")
-        self.taps = int(p.get("conv_taps") or 1)
+        self.has_conv, self.taps = p.get("conv_taps") is not None, int(p.get("conv_taps") or 1)
         self.qkv_bias, self.out_bias, self.head_gate = bool(p.get("qkv_bias", False)), bool(p.get("out_bias", False)), bool(p.get("head_gate", False))
         self.nq, self.nk, self.nvv = self.nh * self.dk, self.nkv * self.dk, self.nkv * self.dv
         self.n_conv = self.nq + self.nk + self.nvv
@@ -66,7 +66,7 @@ class ConvGatedAttention(Mixer):
             specs += [WeightSpec(n + ".b", (c,), "vector", ("normal", 0.02)) for n, c in (("q", self.nq), ("k", self.nk), ("v", self.nvv))]
         if self.out_bias:
             specs.append(WeightSpec("o.b", (H,), "vector", ("normal", 0.02)))
-        if self.taps > 1:
+        if self.has_conv:
             specs += [WeightSpec(n + ".conv", (c, self.taps), "vector", ("normal", 0.5)) for n, c in (("q", self.nq), ("k", self.nk), ("v", self.nvv))]
         if self.head_gate:
             specs.append(WeightSpec("g", (self.nh, H)))
@@ -83,7 +83,7 @@ class ConvGatedAttention(Mixer):
                            torch.zeros(self.n_proj_pad - self.n_conv, dtype=torch.float32, device=t["q"].device)])
         self.proj.set(torch.cat(ws, dim=0), b)
         self.o_proj.set(t["o"], t.get("o.b"))
-        if self.taps > 1:
+        if self.has_conv:
             self.conv.set([t["q.conv"], t["k.conv"], t["v.conv"]])
         else:
             self.conv.set([torch.ones((self.n_conv, 1), dtype=torch.float32, device=t["q"].device)])

@@ -79,7 +79,8 @@ class GatedDeltaRule(Mixer):
         super().__init__(params, prefix, dtype)
         p = params
         self.hidden, self.nh, self.ng = int(p["hidden"]), int(p["n_heads"]), int(p["n_qk_heads"])
-        self.dk, self.dv, self.taps = int(p["qk_dim"]), int(p["v_dim"]), int(p.get("conv_taps") or 1)
+        self.dk, self.dv = int(p["qk_dim"]), int(p["v_dim"])
+        self.has_conv, self.taps = p.get("conv_taps") is not None, int(p.get("conv_taps") or 1)
         if self.nh <= 0 or self.ng <= 0 or self.nh % self.ng:
             raise ValueError(f"delta rule: {self.nh} value heads are not a multiple of {self.ng} q/k heads")
         self.eps, self.unit_eps = float(p["eps"]), float(p.get("unit_eps", 1e-6))
@@ -98,7 +99,7 @@ class GatedDeltaRule(Mixer):
                  WeightSpec("b", (self.nh, H)), WeightSpec("a", (self.nh, H)), WeightSpec("g", (self.nv, H)), WeightSpec("o", (H, self.nv)),
                  WeightSpec("A_log", (self.nh,), "vector", ("normal", 0.5)), WeightSpec("dt_bias", (self.nh,), "vector", ("normal", 0.5)),
                  WeightSpec("norm", (self.dv,), "vector", ("ones_normal", 0.05))]
-        if self.taps > 1:
+        if self.has_conv:
             specs += [WeightSpec(n + ".conv", (c, self.taps), "vector", ("normal", 0.5)) for n, c in (("q", self.nqk), ("k", self.nqk), ("v", self.nv))]
         return specs
 
@@ -108,7 +109,7 @@ class GatedDeltaRule(Mixer):
             ws.append(torch.zeros((self.n_proj_pad - self.n_proj, self.hidden), dtype=ws[0].dtype, device=ws[0].device))
         self.proj.set(torch.cat(ws, dim=0))
         self.o_proj.set(t["o"])
-        if self.taps > 1:
+        if self.has_conv:
             self.conv.set([t["q.conv"], t["k.conv"], t["v.conv"]])
         else:
             self.conv.set([torch.ones((self.n_conv, 1), dtype=torch.float32, device=t["q"].device)])

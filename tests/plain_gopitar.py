@@ -79,11 +79,13 @@ def conv_gated_attention(h, p, c):
     q = h @ p["q"].T + p["q.b"]
     k = h @ p["k"].T + p["k.b"]
     v = h @ p["v"].T + p["v.b"]
-    q, k, v = short_conv(q, p["q.conv"]), short_conv(k, p["k.conv"]), short_conv(v, p["v.conv"])
+    if c.get("conv") is not None:
+        q, k, v = short_conv(q, p["q.conv"]), short_conv(k, p["k.conv"]), short_conv(v, p["v.conv"])
     pos = torch.arange(T)
-    q = rotate_half(q.view(T, H, d), pos, c["rot"]["dims"], c["rot"]["base"])
-    k = rotate_half(k.view(T, G, d), pos, c["rot"]["dims"], c["rot"]["base"])
-    o = window_softmax_attention(q, k, v.view(T, G, dv), c["scale"], c["mask"]["size"])
+    rot = c.get("rot") or {"dims": 0, "base": 1.0}
+    q = rotate_half(q.view(T, H, d), pos, rot["dims"], rot["base"])
+    k = rotate_half(k.view(T, G, d), pos, rot["dims"], rot["base"])
+    o = window_softmax_attention(q, k, v.view(T, G, dv), c["scale"], c["mask"]["size"] if c.get("mask") else None)
     gate = torch.sigmoid(h @ p["g"].T)                         # [T, H]
     o = o * gate[:, :, None]
     return o.reshape(T, H * dv) @ p["o"].T + p["o.b"]
@@ -140,9 +142,10 @@ def gated_delta_rule(q, k, v, beta, g):
 def delta_mixer(h, p, c, eps):
     T = h.shape[0]
     H, G, d, dv = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
-    q = silu(short_conv(h @ p["q"].T, p["q.conv"])).view(T, G, d)
-    k = silu(short_conv(h @ p["k"].T, p["k.conv"])).view(T, G, d)
-    v = silu(short_conv(h @ p["v"].T, p["v.conv"])).view(T, H, dv)
+    q, k, v = h @ p["q"].T, h @ p["k"].T, h @ p["v"].T
+    if c.get("conv") is not None:
+        q, k, v = short_conv(q, p["q.conv"]), short_conv(k, p["k.conv"]), short_conv(v, p["v.conv"])
+    q, k, v = silu(q).view(T, G, d), silu(k).view(T, G, d), silu(v).view(T, H, dv)
     q = unit(q) * d ** -0.5
     k = unit(k)
     rep = H // G
