@@ -157,7 +157,8 @@ IL_EXPORT int il_delta_prep(float* qk, int ld, int q_off, int k_off, int G, int 
 //   MODE 0 (decayed sum):  S = decay_h S + k v^T;                               o = S^T q
 //   MODE 1 (delta rule):   S = g_t S;  u = beta_t (v - S^T k);  S = S + k u^T;   o = S^T q
 // q and k of SM_CHUNK tokens are staged in shared memory at a time. `in_act` 1: silu on q, k, v as they are read.
-// q/k head of value head h: h / (H / G).
+// q/k head of value head h: h / (H / G). This form takes every size; key sizes up to 256 run the register form below
+// (`generic` 0), which gives the same sums in another order.
 #define SM_CHUNK 8
 template <int MODE>
 __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld_q,
@@ -227,13 +228,185 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
     }
 }
 
+// The same recurrences with the state in registers. A column of S is shared by `split` neighbouring lanes, each holding
+// DPT of its rows (rows beyond dim are padding: their q and k are staged as zeros, so they stay zero); the dot products
+// S^T k and S^T q are finished by xor-shuffles among those lanes. A block is 128 threads = 128 / split columns of one head
+// of one entry. q, k, v (and the delta rule's g and beta) of SR_CHUNK tokens are staged in shared memory; the next
+// chunk's values are loaded into registers while the current chunk is computed, so the token loop waits for no global
+// load. Per token the critical path is one multiply, one dot product of DPT terms, log2(split) shuffles and one update.
+#define SR_CHUNK 8
+#define SR_THREADS 128
+template <int MODE, int DPT>
+__global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
+    const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld_q, int ld_k, int ld_v, int H, int G,
+    int dim, int vdim, int in_act, const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
+    float* state, size_t slot_stride, const int* __restrict__ read_slots, const int* __restrict__ write_slots,
+    const int* __restrict__ qstart, float* __restrict__ out, int ldo, int log_split) {
+    extern __shared__ float sm[];
+    const int split = 1 << log_split, dimp = DPT << log_split, log_dimp = log_split + (DPT == 8 ? 3 : DPT == 16 ? 4 : 5);
+    const int cpb = SR_THREADS >> log_split, log_cpb = 7 - log_split;
+    float* qs = sm;                               // [SR_CHUNK][dimp]
+    float* ks = qs + SR_CHUNK * dimp;             // [SR_CHUNK][dimp]
+    float* vs = ks + SR_CHUNK * dimp;             // [SR_CHUNK][cpb]
+    float* gb = vs + SR_CHUNK * cpb;              // [2][SR_CHUNK]: g, beta
+    const int e = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int part = tid & (split - 1), col_l = tid >> log_split, c = blockIdx.z * cpb + col_l;
+    const int q0 = qstart[e], n = qstart[e + 1] - q0;
+    if (n <= 0) return;
+    const int hq = h / (H / G);
+    const bool live = c < vdim;
+    const int d0 = part * DPT;
+    float S[DPT];
+    {
+        const float* rd = state + (size_t)read_slots[e] * slot_stride + (size_t)h * dim * vdim;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) S[i] = (live && d0 + i < dim) ? rd[(size_t)(d0 + i) * vdim + c] : 0.f;
+    }
+    const float dec = MODE == 0 ? decay[h] : 0.f;
+    constexpr int NQ = SR_CHUNK * DPT * 8 / SR_THREADS;    // staged q (and k) values per thread at the widest split (8)
+    constexpr int NV = SR_CHUNK;                           // staged v values per thread at split 1
+    float qr[NQ], kr[NQ], vr[NV], gr = 0.f;
+    const int n_qk = SR_CHUNK << log_dimp, n_v = SR_CHUNK << log_cpb;
+
+    auto fetch = [&](int t0) {                    // the chunk's values into registers (zeros beyond the entry's end and in padding)
+        const int nt = min(SR_CHUNK, n - t0);
+#pragma unroll
+        for (int j = 0; j < NQ; ++j) {
+            const int idx = tid + j * SR_THREADS;
+            const int tt = idx >> log_dimp, d = idx & (dimp - 1);
+            const bool ok = idx < n_qk && tt < nt && d < dim;
+            const size_t row = (size_t)(q0 + t0 + tt);
+            qr[j] = ok ? q[row * ld_q + hq * dim + d] : 0.f;
+            kr[j] = ok ? k[row * ld_k + hq * dim + d] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int idx = tid + j * SR_THREADS;
+            const int tt = idx >> log_cpb, cc = blockIdx.z * cpb + (idx & (cpb - 1));
+            vr[j] = (idx < n_v && tt < nt && cc < vdim) ? v[(size_t)(q0 + t0 + tt) * ld_v + h * vdim + cc] : 0.f;
+        }
+        if (MODE == 1 && tid < 2 * SR_CHUNK) {
+            const int tt = tid & (SR_CHUNK - 1);
+            gr = tt < nt ? (tid < SR_CHUNK ? gdec : beta)[(size_t)(q0 + t0 + tt) * H + h] : 0.f;
+        }
+    };
+    auto stage = [&]() {                          // registers to shared memory, the activation applied once per value
+#pragma unroll
+        for (int j = 0; j < NQ; ++j) {
+            const int idx = tid + j * SR_THREADS;
+            if (idx < n_qk) {
+                qs[idx] = in_act ? sm_silu(qr[j]) : qr[j];
+                ks[idx] = in_act ? sm_silu(kr[j]) : kr[j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int idx = tid + j * SR_THREADS;
+            if (idx < n_v) vs[idx] = in_act ? sm_silu(vr[j]) : vr[j];
+        }
+        if (MODE == 1 && tid < 2 * SR_CHUNK) gb[tid] = gr;
+    };
+
+    fetch(0);
+    stage();
+    __syncthreads();
+    for (int t0 = 0; t0 < n; t0 += SR_CHUNK) {
+        const int nt = min(SR_CHUNK, n - t0);
+        if (t0 + SR_CHUNK < n) fetch(t0 + SR_CHUNK);
+        for (int tt = 0; tt < nt; ++tt) {
+            const float4* qq = reinterpret_cast<const float4*>(qs + (tt << log_dimp) + d0);
+            const float4* kk = reinterpret_cast<const float4*>(ks + (tt << log_dimp) + d0);
+            const float vc = vs[(tt << log_cpb) + col_l];
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+            if (MODE == 0) {
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 k4 = kk[i], q4 = qq[i];
+                    S[4 * i] = fmaf(dec, S[4 * i], k4.x * vc);
+                    S[4 * i + 1] = fmaf(dec, S[4 * i + 1], k4.y * vc);
+                    S[4 * i + 2] = fmaf(dec, S[4 * i + 2], k4.z * vc);
+                    S[4 * i + 3] = fmaf(dec, S[4 * i + 3], k4.w * vc);
+                    o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                    o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                }
+            } else {
+                const float g = gb[tt], bt = gb[SR_CHUNK + tt];
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 k4 = kk[i];
+                    S[4 * i] *= g, S[4 * i + 1] *= g, S[4 * i + 2] *= g, S[4 * i + 3] *= g;
+                    s0 = fmaf(S[4 * i], k4.x, s0), s1 = fmaf(S[4 * i + 1], k4.y, s1);
+                    s2 = fmaf(S[4 * i + 2], k4.z, s2), s3 = fmaf(S[4 * i + 3], k4.w, s3);
+                }
+                float sk = (s0 + s1) + (s2 + s3);
+                for (int m = split >> 1; m > 0; m >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, m);
+                const float u = bt * (vc - sk);
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 k4 = kk[i], q4 = qq[i];
+                    S[4 * i] = fmaf(k4.x, u, S[4 * i]);
+                    S[4 * i + 1] = fmaf(k4.y, u, S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(k4.z, u, S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(k4.w, u, S[4 * i + 3]);
+                    o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                    o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                }
+            }
+            float o = (o0 + o1) + (o2 + o3);
+            for (int m = split >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+            if (live && part == 0) out[(size_t)(q0 + t0 + tt) * ldo + h * vdim + c] = o;
+        }
+        __syncthreads();                          // everyone has read this chunk
+        if (t0 + SR_CHUNK < n) stage();
+        __syncthreads();
+    }
+    if (live) {
+        float* wr = state + (size_t)write_slots[e] * slot_stride + (size_t)h * dim * vdim;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i)
+            if (d0 + i < dim) wr[(size_t)(d0 + i) * vdim + c] = S[i];
+    }
+}
+
+template <int MODE, int DPT>
+static void sr_launch(dim3 grid, size_t smem, cudaStream_t stream, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v,
+                      int H, int G, int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
+                      size_t slot_stride, const int* read_slots, const int* write_slots, const int* qstart, float* out, int ldo, int log_split) {
+    matrix_state_scan_reg_kernel<MODE, DPT><<<grid, SR_THREADS, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec,
+                                                                                state, slot_stride, read_slots, write_slots, qstart, out, ldo,
+                                                                                log_split);
+}
+
 IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v, int H, int G,
                                    int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
                                    long long slot_stride, const int* read_slots, const int* write_slots, const int* qstart, int E,
-                                   float* out, int ldo, cudaStream_t stream) {
+                                   float* out, int ldo, int generic, cudaStream_t stream) {
     if (E <= 0) return IL_OK;
     if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1)) return IL_BAD_ARG;
     if (mode == 0 ? !decay : (!beta || !gdec)) return IL_BAD_ARG;
+    if (dim <= 256 && !generic) {
+        // rows of a column per lane (8, 16 or 32) and lanes per column (a power of two up to 8) that cover dim
+        const int dpt = dim <= 32 ? 8 : dim <= 128 ? 16 : 32;
+        int log_split = 0;
+        while ((dpt << log_split) < dim) ++log_split;
+        const int dimp = dpt << log_split, cpb = SR_THREADS >> log_split;
+        const size_t smem_r = ((size_t)SR_CHUNK * (2 * dimp + cpb) + 2 * SR_CHUNK) * sizeof(float);
+        const dim3 grid_r(E, H, (vdim + cpb - 1) / cpb);
+#define SR_ARGS grid_r, smem_r, stream, q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state, (size_t)slot_stride, \
+                read_slots, write_slots, qstart, out, ldo, log_split
+        if (mode == 0) {
+            if (dpt == 8) sr_launch<0, 8>(SR_ARGS);
+            else if (dpt == 16) sr_launch<0, 16>(SR_ARGS);
+            else sr_launch<0, 32>(SR_ARGS);
+        } else {
+            if (dpt == 8) sr_launch<1, 8>(SR_ARGS);
+            else if (dpt == 16) sr_launch<1, 16>(SR_ARGS);
+            else sr_launch<1, 32>(SR_ARGS);
+        }
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
     int ncol = vdim >= 128 ? 128 : vdim > 32 ? 64 : 32;
     size_t smem = ((size_t)dim * ncol + 2 * SM_CHUNK * dim) * sizeof(float);
     while (smem > 200 * 1024 && ncol > 32) {

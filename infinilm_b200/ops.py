@@ -1039,12 +1039,13 @@ SCAN_DECAY, SCAN_DELTA = 0, 1
 def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n_qk_heads: int, dim: int,
                       vdim: int, in_act: int, decay: Optional[torch.Tensor], beta: Optional[torch.Tensor],
                       gdec: Optional[torch.Tensor], state: torch.Tensor, read_slots: torch.Tensor, write_slots: torch.Tensor,
-                      entry_qstart: torch.Tensor, n_entries: int, out: torch.Tensor) -> None:
+                      entry_qstart: torch.Tensor, n_entries: int, out: torch.Tensor, generic: bool = False) -> None:
     """A recurrence over a float32 state S [dim, vdim] per (request, head), token by token in each entry's order.
     SCAN_DECAY: S = decay[h] S + k v^T, o = S^T q. SCAN_DELTA: S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q.
     q, k float32 [T, >= n_qk_heads*dim] (views with a row stride), v float32 [T, >= n_heads*vdim], out float32 [T, n_heads*vdim];
     value head h reads q/k head h // (n_heads // n_qk_heads). in_act 1: silu on q, k, v as read.
-    state float32 [slots, n_heads, dim, vdim]."""
+    state float32 [slots, n_heads, dim, vdim]. `generic`: the kernel that keeps the state in shared memory (any size; the
+    one that runs beyond a key size of 256) instead of the one that keeps it in registers."""
     _need_cuda(q, k, v, decay, beta, gdec, state, read_slots, write_slots, entry_qstart, out)
     _i32("matrix_state_scan", read_slots, write_slots, entry_qstart)
     for t in (q, k, v, out, state):
@@ -1056,10 +1057,10 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
         raise KernelError("matrix_state_scan: shapes")
     f = _fn("seqmix", "il_matrix_state_scan", [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p,
-                                               _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p])
+                                               _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
     _check(f(mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), n_heads, n_qk_heads, dim, vdim, in_act,
              _ptr(decay), _ptr(beta), _ptr(gdec), _ptr(state), state.stride(0), _ptr(read_slots), _ptr(write_slots),
-             _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), _stream()), "matrix_state_scan")
+             _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), int(generic), _stream()), "matrix_state_scan")
 
 
 GATE_SIGMOID, GATE_SILU = 0, 1

@@ -1,0 +1,243 @@
+"""Gopitar through the engine against the plain implementation under every way of cutting the work: whole prompts; a
+prompt and then its last tokens one by one (long decoding, the window passing over decoded tokens); portions of changing
+size down to two tokens and one; up to four live requests mixed, unequal, with so few pages and state slots that both are
+used again; keys just inside and just outside the window and at page borders, made to stand out; a token far back that only
+the recurrent state can carry; greedy generation through `LLM.generate` and the scheduler; and the trace runner as a process."""
+import json
+import os
+import subprocess
+import sys
+import warnings
+
+import pytest
+import torch
+
+import plain_gopitar as P
+from gopitar_configs import GOPITAR, make_weights, token_ids
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 4e-5, "bfloat16": 5e-2}
+LENGTHS = {"a": [1, 2, 23, 24, 25, 70, 130], "b": [3, 33, 34, 100], "c": [1, 16, 17, 90], "d": [2, 50, 150]}
+CASES = [("a", 0), ("b", 1), ("c", 2), ("d", 3)]
+DTYPES = ["float32", "bfloat16"]
+
+
+def _engine(raw, w, dtype, num_pages=48, max_seqs=4, max_batch_tokens=512):
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.engine import Engine
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", RuntimeWarning)
+        return Engine.from_tensors(config_from_json(raw), w, dtype=dtype, page_size=16, num_pages=num_pages, max_seqs=max_seqs,
+                                   max_batch_tokens=max_batch_tokens)
+
+
+_oracle_cache = {}
+
+
+def _oracle(name, seed, ids):
+    key = (name, seed, tuple(ids))
+    if key not in _oracle_cache:
+        raw = GOPITAR[name]()
+        _oracle_cache[key] = P.forward(raw, make_weights(raw, seed), ids)
+    return _oracle_cache[key]
+
+
+def _check(got, ref, dtype, what):
+    got, ref = got.double().cpu(), ref.double()
+    assert got.shape == ref.shape and torch.isfinite(got).all(), what
+    err = ((got - ref).abs() / ref.abs().amax(dim=-1, keepdim=True)).amax(dim=-1)
+    bad = torch.nonzero(err > TOL[dtype])
+    n = ref.shape[0]
+    allowed = 0 if dtype == "float32" else n // 25
+    worst = float(err.max()) if n else 0.0
+    assert bad.numel() <= allowed and (dtype == "float32" or worst <= 3 * TOL[dtype]), \
+        f"{what}: first wrong position {int(bad[0])} of {n} (rel err {float(err[int(bad[0])]):.2e}, worst {worst:.2e}, {bad.numel()} wrong)"
+
+
+def _run_cut(eng, ids, cuts, seq_id="r"):
+    from infinilm_b200.engine import StepEntry
+    assert sum(cuts) == len(ids)
+    seq, outs, a = eng.open(seq_id), [], 0
+    for c in cuts:
+        outs.append(eng.step([StepEntry(seq, ids[a:a + c], list(range(c)))]).clone())
+        a += c
+    eng.close(seq)
+    return torch.cat(outs, 0)
+
+
+def _run_schedule(eng, requests, schedule):
+    from infinilm_b200.engine import StepEntry
+    done, seqs, outs = {k: 0 for k in requests}, {}, {k: [] for k in requests}
+    for step in schedule:
+        entries = []
+        for rid, n in step:
+            if rid not in seqs:
+                seqs[rid] = eng.open(rid)
+            entries.append(StepEntry(seqs[rid], requests[rid][done[rid]:done[rid] + n], list(range(n))))
+            done[rid] += n
+        logits, r = eng.step(entries).clone(), 0
+        for rid, n in step:
+            outs[rid].append(logits[r:r + n])
+            r += n
+            if done[rid] == len(requests[rid]):
+                eng.close(seqs.pop(rid))
+        eng.cache.check_invariants()
+    assert all(done[k] == len(requests[k]) for k in requests)
+    return {k: torch.cat(v, 0) for k, v in outs.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_whole_prompts(cuda_device, name, seed, dtype):
+    raw = GOPITAR[name]()
+    eng = _engine(raw, make_weights(raw, seed), dtype)
+    for n in LENGTHS[name]:
+        ids = token_ids(n, raw["vocab"], 100 + n)
+        _check(_run_cut(eng, ids, [n]), _oracle(name, seed, ids), dtype, f"{name} whole prompt of {n}")
+    eng.synchronize()
+    eng.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_prompt_then_token_by_token(cuda_device, name, seed, dtype):
+    """Prefill against decoding through the cache and the states: the last 60 tokens one by one (longer than every window
+    but one, so the window passes over decoded tokens); and a sequence decoded from its very first token on."""
+    raw = GOPITAR[name]()
+    eng = _engine(raw, make_weights(raw, seed), dtype)
+    ids = token_ids(110, raw["vocab"], 7)
+    _check(_run_cut(eng, ids, [50] + [1] * 60), _oracle(name, seed, ids), dtype, f"{name} 50 + 60 x 1")
+    ids = token_ids(45, raw["vocab"], 8)
+    _check(_run_cut(eng, ids, [1] * 45), _oracle(name, seed, ids), dtype, f"{name} 45 x 1")
+    eng.synchronize()
+    eng.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_portions_of_changing_size(cuda_device, name, seed, dtype):
+    raw = GOPITAR[name]()
+    eng = _engine(raw, make_weights(raw, seed), dtype)
+    ids = token_ids(131, raw["vocab"], 9)
+    ref = _oracle(name, seed, ids)
+    for cuts in ([2, 2, 3, 16, 1, 31, 17, 2, 40, 15, 2], [64, 64, 3], [5] * 26 + [1], [15, 1, 16, 32, 33, 34]):
+        _check(_run_cut(eng, ids, cuts), ref, dtype, f"{name} portions {cuts[:6]}")
+    eng.synchronize()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_mixed_batches_reuse_pages_and_slots(cuda_device, name, seed, dtype):
+    """Five unequal requests through three state slots and a pool that cannot hold them all at once: single tokens beside
+    portions, requests that pause, pages and slots given back and taken again."""
+    raw = GOPITAR[name]()
+    windowed = name != "d"
+    eng = _engine(raw, make_weights(raw, seed), dtype, num_pages=14 if windowed else 20, max_seqs=3)
+    req = {k: token_ids(n, raw["vocab"], 20 + i) for i, (k, n) in enumerate((("p", 90), ("q", 37), ("r", 3), ("s", 70), ("t", 18)))}
+    schedule = [[("p", 40), ("q", 2)], [("p", 1), ("q", 1), ("r", 2)], [("q", 30), ("p", 1)], [("r", 1), ("p", 17), ("q", 1)],
+                [("p", 1), ("q", 1), ("s", 33)], [("s", 1), ("p", 20), ("q", 2)], [("s", 2), ("p", 10), ("t", 17)], [("s", 34), ("t", 1)]]
+    got = _run_schedule(eng, req, schedule)
+    for k, ids in req.items():
+        _check(got[k], _oracle(name, seed, ids), dtype, f"{name} mixed, request {k}")
+    eng.synchronize()
+    assert len(eng.cache.live) == 0 and all(n == grp.pool.n_pages for grp in eng.cache.groups if grp.pool for n in [grp.pool.n_free])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_keys_at_the_windows_edge_and_at_page_borders(cuda_device, dtype):
+    """One token with an embedding far from the others stands at every distance around the window (24) and around page
+    borders from the token whose logits are compared: it is seen at distance window - 1, not at distance window - in a
+    prompt, in portions and decoded alone."""
+    raw = GOPITAR["a"]()
+    w = make_weights(raw, 11)
+    w["embed"][5] = (w["embed"][5].float() * 6.0).to(torch.bfloat16)        # the marked token
+    eng = _engine(raw, w, dtype)
+    base = [t if t != 5 else 6 for t in token_ids(80, raw["vocab"], 12)]
+    for at in (15, 16, 17, 31, 32, 39, 40, 41, 47, 48, 55, 56, 57, 63, 64):
+        ids = list(base)
+        ids[at] = 5
+        ref = P.forward(raw, w, ids)
+        for cuts in ([80], [at + 1] + [1] * (79 - at), [at, 2] + [1] * (78 - at) if at + 2 <= 80 else [80], [33, 31, 16]):
+            if sum(cuts) != 80:
+                continue
+            _check(_run_cut(eng, ids, cuts), ref, dtype, f"marker at {at}, cuts {cuts[:3]}")
+    eng.synchronize()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_token_reaches_the_end_through_the_states_only(cuda_device, dtype):
+    """The window is 24; a change of the first token must still move the logits 300 tokens later (decays near one), and
+    the engine must follow the plain implementation there, whole and decoded."""
+    raw = GOPITAR["a"]()
+    w = make_weights(raw, 13)
+    ids = token_ids(300, raw["vocab"], 14)
+    other = [(ids[0] + 1) % raw["vocab"]] + ids[1:]
+    ref, ref2 = P.forward(raw, w, ids), P.forward(raw, w, other)
+    assert float((ref[-1] - ref2[-1]).abs().max()) > 1e-3 * float(ref[-1].abs().max())       # the states carry it
+    eng = _engine(raw, w, dtype)
+    _check(_run_cut(eng, ids, [300])[-40:], ref[-40:], dtype, "far token, whole")
+    _check(_run_cut(eng, other, [260] + [1] * 40)[-40:], ref2[-40:], dtype, "far token, decoded")
+    eng.synchronize()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_llm(cuda_device, dtype):
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.llm import LLM, SamplingParams
+    raw = GOPITAR["c"]()
+    w = make_weights(raw, 4)
+    prompts = [token_ids(n, raw["vocab"], 30 + n) for n in (5, 21, 40)]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", RuntimeWarning)
+        llm = LLM.from_tensors(config_from_json(raw), w, dtype=dtype, num_blocks=40, block_size=16, max_batch_size=3)
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(top_k=1, max_tokens=24, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        got = list(o.outputs[0].token_ids)
+        assert len(got) == 24
+        ids = list(p)
+        for t in got:                             # every token is the plain implementation's argmax, where that is clear
+            lg = P.forward(raw, w, ids)[-1]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) > (1e-3 if dtype == "float32" else 0.2 * float(lg.abs().max())):
+                assert t == int(torch.argmax(lg)), f"token {len(ids) - len(p)}"
+            ids.append(t)
+    llm.close()
+
+
+def test_trace_runner_as_a_process(cuda_device, tmp_path):
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.weights import write_model_folder
+    raw = GOPITAR["b"]()
+    folder = write_model_folder(config_from_json(raw), 6, str(tmp_path / "m"))
+    from infinilm_b200.weights.safetensors_io import SafetensorsFile
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    w = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    req = {k: token_ids(n, raw["vocab"], 40 + n) for k, n in (("a", 70), ("b", 9), ("c", 33), ("d", 50), ("e", 20))}
+    steps = [[("a", 30), ("b", 2)], [("a", 1), ("b", 7), ("c", 3)], [("a", 39), ("c", 30), ("d", 1)], [("d", 49), ("e", 20)]]
+    done, lines, wants = {k: 0 for k in req}, [], []
+    for n, st in enumerate(steps):
+        entries, end = [], []
+        for rid, c in st:
+            a = done[rid]
+            entries.append({"id": rid, "tokens": req[rid][a:a + c], "want": [0, c - 1] if c > 1 else [0]})
+            wants.append([(rid, a), (rid, a + c - 1)] if c > 1 else [(rid, a)])
+            done[rid] = a + c
+            if done[rid] == len(req[rid]):
+                end.append(rid)
+        lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out_dir = str(tmp_path / "out")
+    for dtype in ("float32", "bfloat16"):
+        p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", out_dir,
+                            "--max-tokens", "192"], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=900)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {n}" for n in range(len(steps))]
+        ref = {k: P.forward(raw, w, ids) for k, ids in req.items()}
+        k0 = 0
+        for n, st in enumerate(steps):
+            rows = [x for e in wants[k0:k0 + len(st)] for x in e]
+            k0 += len(st)
+            got = torch.frombuffer(bytearray(open(os.path.join(out_dir, f"{n}.f32"), "rb").read()), dtype=torch.float32).view(len(rows), raw["vocab"])
+            _check(got, torch.stack([ref[rid][pos] for rid, pos in rows]), dtype, f"trace step {n} ({dtype})")
