@@ -175,7 +175,8 @@ def timeline_step(args) -> int:
     raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)
     raw["num_hidden_layers"] = args.layers or 4
     if args.design != "default":                  # one of the pair of `--workload designs`, at the first of --design-sizes
-        raw = design_pair(args.design_sizes.split(",")[0], args.layers or 4)[0 if args.design == "nirozen" else 1]
+        pair = gopitar_pair if args.design == "gopitar" else design_pair
+        raw = pair(args.design_sizes.split(",")[0], args.layers or 4)[1 if args.design == "dense" else 0]
         raw["num_hidden_layers"] = args.layers or 4
     cfg = config_from_json(raw)
     B, P = args.batch, args.prompt_len
@@ -290,6 +291,23 @@ def design_pair(size: str, layers: int):
     return nz, dense
 
 
+def gopitar_pair(size: str, layers: int):
+    """(Gopitar configuration, MiniCPM4 configuration of the same width, depth, heads, head size, vocabulary and feed-forward
+    width.) Three layers in four mix by windowed softmax attention (2 kv heads, window 1,024, 4 taps) beside decayed linear
+    attention, the fourth by the gated delta rule; head sizes of published models of these kinds (128; 64 at the small width)."""
+    W, H, d, ff, V = {"1k": (1024, 8, 64, 3072, 32000), "2k": (2048, 16, 128, 8192, 32000), "4k": (4096, 32, 128, 12288, 32000)}[size]
+    left = {"heads": H, "kv_heads": 2, "dim": d, "vdim": d, "conv": 4, "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": d},
+            "scale": d ** -0.5}
+    right = {"heads": H, "dim": d, "vdim": d, "decay": [1.0 - 2.0 ** (-5 - 3 * i / max(H - 1, 1)) for i in range(H)]}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}, "mlp": {"kind": "dense", "ff": ff}}
+    delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": max(H // 2, 1), "dim": d, "vdim": d, "conv": 4}, "mlp": {"kind": "dense", "ff": ff}}
+    gp = {"architecture": "Gopitar", "vocab": V, "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
+          "layers": [dict(delta) if i % 4 == 2 else dict(par) for i in range(layers)]}
+    dense = dict(CONFIG_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=2, head_dim=d,
+                 intermediate_size=ff, vocab_size=V, rope_scaling=None, max_position_embeddings=32768, eos_token_id=[2])
+    return gp, dense
+
+
 class OpTimer:
     """Brackets every kernel wrapper of `infinilm_b200.ops`, every library product of `Linear` and the library's grouped
     product with CUDA events on the launching stream, for steps that run eagerly; `table()` gives microseconds and calls per name."""
@@ -308,6 +326,8 @@ class OpTimer:
             out = fn(*a, **k)
             e1.record()
             lab = label or name
+            if lab == "matrix_state_scan":
+                lab += " delta" if a[0] == 1 else " decay"
             if lab == "linear":
                 x = a[1] if len(a) > 1 else k["x"]
                 lab = f"linear[{a[0].out_features}x{a[0].in_features}]" + ("" if x.shape[0] > 16 else " skinny")
@@ -326,7 +346,8 @@ class OpTimer:
         from infinilm_b200.parts.linear import Linear
         for name in ("embed", "embed_pair_pos", "add_rmsnorm", "swiglu", "rope_store", "attention_plain", "attention_decode",
                      "attention_prefill", "attention_prefill_tc5", "gemm_skinny", "gemm_skinny_resid", "gemm_skinny_rope", "gemm_mid",
-                     "gemm_tc5", "latent_norm_store", "moe_route", "moe_sort", "moe_combine", "gather_rows", "gemm_grouped"):
+                     "gemm_tc5", "latent_norm_store", "moe_route", "moe_sort", "moe_combine", "gather_rows", "gemm_grouped", "short_conv",
+                     "short_conv_state", "delta_prep", "matrix_state_scan", "group_norm_gate", "head_gate", "scaled_sum", "softcap"):
             self._wrap(ops, name)
         self._wrap(Linear, "__call__", "linear")
         if hasattr(F, "grouped_mm"):
@@ -363,7 +384,9 @@ def run_designs(args) -> int:
     P = PROMPT_LEN
     for size in args.design_sizes.split(","):
         rec = {"workload": "designs", "size": size, "layers": L, "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}}
-        for which, raw in zip(("nirozen", "dense_gqa"), design_pair(size, L)):
+        family = getattr(args, "design_family", "nirozen")
+        rec["design"] = family
+        for which, raw in zip((family, "dense_gqa"), gopitar_pair(size, L) if family == "gopitar" else design_pair(size, L)):
             cfg = config_from_json(raw)
             B = 64
             eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
@@ -449,8 +472,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
     ap.add_argument("--points", type=str, default="1,64", help="batch sizes of the extra decode points")
-    ap.add_argument("--design", choices=["default", "nirozen", "dense"], default="default",
+    ap.add_argument("--design", choices=["default", "nirozen", "gopitar", "dense"], default="default",
                     help="--timeline: the step of one of the pair of --workload designs instead of the benchmark model")
+    ap.add_argument("--design-family", choices=["nirozen", "gopitar"], default="nirozen",
+                    help="--workload designs: which design stands beside the dense GQA model of equal size")
     ap.add_argument("--design-sizes", type=str, default="1k,2k", help="--workload designs: layer sizes to run (1k, 2k, 4k)")
     ap.add_argument("--workload", choices=["default", "long_context", "continuous", "designs"], default="default",
                     help="default: the benchmark line. long_context: 8 requests x 16,384-token prompts at 8B sizes, prompt "
