@@ -12,6 +12,10 @@ __device__ __forceinline__ float sm_silu(float z) { return z / (1.f + expf(-z));
 __device__ __forceinline__ float sm_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float sm_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
+// SiLU by the fast exponential and division (relative error near 2^-21): the one the recurrences apply to their inputs,
+// in the kernel or as a pass of its own, so that a token's state does not depend on which of the two ran.
+__device__ __forceinline__ float sm_silu_fast(float z) { return __fdividef(z, 1.f + __expf(-z)); }
+
 #define SM_MAX_TAPS 16
 
 // ---- short convolution ----------------------------------------------------------------------------------------------
@@ -152,8 +156,9 @@ IL_EXPORT int il_delta_prep(float* qk, int ld, int q_off, int k_off, int G, int 
 }
 
 // ---- recurrences over a matrix state --------------------------------------------------------------------------------
-// State S [dim, vdim] per (request, head), float32. A block owns `blockDim.x` columns of one head of one entry, one column a
-// thread, the column in shared memory (column c of row d at s[d * ncol + c]: no bank is shared). Tokens in order:
+// State S [dim, vdim] per (request, head), float32, stored column by column ([vdim][dim]: the dim entries that one output
+// column needs lie together). A block owns `blockDim.x` columns of one head of one entry, one column a
+// thread, the column in shared memory (column c of row d at s[d * (ncol + 1) + c]: no bank is shared). Tokens in order:
 //   MODE 0 (decayed sum):  S = decay_h S + k v^T;                               o = S^T q
 //   MODE 1 (delta rule):   S = g_t S;  u = beta_t (v - S^T k);  S = S + k u^T;   o = S^T q
 // q and k of SM_CHUNK tokens are staged in shared memory at a time. `in_act` 1: silu on q, k, v as they are read.
@@ -166,19 +171,25 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
                                          const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
                                          float* state, size_t slot_stride, const int* __restrict__ read_slots,
                                          const int* __restrict__ write_slots, const int* __restrict__ qstart, float* __restrict__ out,
-                                         int ldo) {
+                                         int ldo, int e0) {
     extern __shared__ float sm[];
     const int ncol = blockDim.x;
-    float* S = sm;                                // [dim][ncol]
-    float* qs = sm + (size_t)dim * ncol;          // [SM_CHUNK][dim]
+    const int ncs = ncol + 1;
+    float* S = sm;                                // [dim][ncol + 1]
+    float* qs = sm + (size_t)dim * ncs;           // [SM_CHUNK][dim]
     float* ks = qs + SM_CHUNK * dim;              // [SM_CHUNK][dim]
-    const int e = blockIdx.x, h = blockIdx.y, c = blockIdx.z * ncol + threadIdx.x;
+    const int e = e0 + blockIdx.x, h = blockIdx.y, c = blockIdx.z * ncol + threadIdx.x;
     const int q0 = qstart[e], n = qstart[e + 1] - q0;
     if (n <= 0) return;
     const int hq = h / (H / G);
     const bool live = c < vdim;
+    const int c0 = blockIdx.z * ncol;
     const float* rd = state + (size_t)read_slots[e] * slot_stride + (size_t)h * dim * vdim;
-    for (int d = 0; d < dim; ++d) S[d * ncol + threadIdx.x] = live ? rd[(size_t)d * vdim + c] : 0.f;
+    for (int i = threadIdx.x; i < ncol * dim; i += ncol) {
+        const int cc = i / dim, d = i - cc * dim;
+        S[d * ncs + cc] = c0 + cc < vdim ? rd[(size_t)(c0 + cc) * dim + d] : 0.f;
+    }
+    __syncthreads();
     const float dec = MODE == 0 ? decay[h] : 0.f;
     for (int t0 = 0; t0 < n; t0 += SM_CHUNK) {
         const int nt = min(SM_CHUNK, n - t0);
@@ -187,69 +198,76 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
             const int tt = i / dim, d = i - tt * dim;
             const size_t row = (size_t)(q0 + t0 + tt);
             float a = q[row * ld_q + hq * dim + d], b = k[row * ld_k + hq * dim + d];
-            if (in_act) a = sm_silu(a), b = sm_silu(b);
+            if (in_act) a = sm_silu_fast(a), b = sm_silu_fast(b);
             qs[i] = a, ks[i] = b;
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const size_t row = (size_t)(q0 + t0 + tt);
             float vc = live ? v[row * ld_v + h * vdim + c] : 0.f;
-            if (in_act) vc = sm_silu(vc);
+            if (in_act) vc = sm_silu_fast(vc);
             const float* qq = qs + tt * dim;
             const float* kk = ks + tt * dim;
             float o = 0.f;
             if (MODE == 0) {
                 for (int d = 0; d < dim; ++d) {
-                    const float s = fmaf(dec, S[d * ncol + threadIdx.x], kk[d] * vc);
-                    S[d * ncol + threadIdx.x] = s;
+                    const float s = fmaf(dec, S[d * ncs + threadIdx.x], kk[d] * vc);
+                    S[d * ncs + threadIdx.x] = s;
                     o = fmaf(s, qq[d], o);
                 }
             } else {
                 const float g = gdec[row * H + h], bt = beta[row * H + h];
                 float sk = 0.f;
                 for (int d = 0; d < dim; ++d) {
-                    const float s = g * S[d * ncol + threadIdx.x];
-                    S[d * ncol + threadIdx.x] = s;
+                    const float s = g * S[d * ncs + threadIdx.x];
+                    S[d * ncs + threadIdx.x] = s;
                     sk = fmaf(s, kk[d], sk);
                 }
                 const float u = bt * (vc - sk);
                 for (int d = 0; d < dim; ++d) {
-                    const float s = fmaf(kk[d], u, S[d * ncol + threadIdx.x]);
-                    S[d * ncol + threadIdx.x] = s;
+                    const float s = fmaf(kk[d], u, S[d * ncs + threadIdx.x]);
+                    S[d * ncs + threadIdx.x] = s;
                     o = fmaf(s, qq[d], o);
                 }
             }
             if (live) out[row * ldo + h * vdim + c] = o;
         }
     }
-    if (live) {
-        float* wr = state + (size_t)write_slots[e] * slot_stride + (size_t)h * dim * vdim;
-        for (int d = 0; d < dim; ++d) wr[(size_t)d * vdim + c] = S[d * ncol + threadIdx.x];
+    __syncthreads();
+    float* wr = state + (size_t)write_slots[e] * slot_stride + (size_t)h * dim * vdim;
+    for (int i = threadIdx.x; i < ncol * dim; i += ncol) {
+        const int cc = i / dim, d = i - cc * dim;
+        if (c0 + cc < vdim) wr[(size_t)(c0 + cc) * dim + d] = S[d * ncs + cc];
     }
 }
 
 // The same recurrences with the state in registers. A column of S is shared by `split` neighbouring lanes, each holding
 // DPT of its rows (rows beyond dim are padding: their q and k are staged as zeros, so they stay zero); the dot products
 // S^T k and S^T q are finished by xor-shuffles among those lanes. A block is 128 threads = 128 / split columns of one head
-// of one entry. q, k, v (and the delta rule's g and beta) of SR_CHUNK tokens are staged in shared memory; the next
+// of one entry. q, k, v (and the delta rule's g and beta) of SR_CHUNK tokens (8; 1 in the form for entries that bring a single
+// token, which then needs few registers and many blocks fit an SM) are staged in shared memory; the next
 // chunk's values are loaded into registers while the current chunk is computed, so the token loop waits for no global
 // load. Per token the critical path is one multiply, one dot product of DPT terms, log2(split) shuffles and one update.
-#define SR_CHUNK 8
 #define SR_THREADS 128
-template <int MODE, int DPT>
+#define SR_MAX_SPLIT 16
+template <int MODE, int DPT, int SR_CHUNK>
 __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld_q, int ld_k, int ld_v, int H, int G,
     int dim, int vdim, int in_act, const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
     float* state, size_t slot_stride, const int* __restrict__ read_slots, const int* __restrict__ write_slots,
-    const int* __restrict__ qstart, float* __restrict__ out, int ldo, int log_split) {
+    const int* __restrict__ qstart, float* __restrict__ out, int ldo, int log_split, int e0) {
     extern __shared__ float sm[];
-    const int split = 1 << log_split, dimp = DPT << log_split, log_dimp = log_split + (DPT == 8 ? 3 : DPT == 16 ? 4 : 5);
+    constexpr int LOG_DPT = DPT == 8 ? 3 : DPT == 16 ? 4 : 5;
+    constexpr int SEG = DPT + 4;                  // a lane's DPT values of q (or k) and 4 floats of padding: the lanes of a column then
+                                                  // read their 16-byte pieces from different banks
+    const int split = 1 << log_split, dimp = DPT << log_split, log_dimp = log_split + LOG_DPT;
     const int cpb = SR_THREADS >> log_split, log_cpb = 7 - log_split;
-    float* qs = sm;                               // [SR_CHUNK][dimp]
-    float* ks = qs + SR_CHUNK * dimp;             // [SR_CHUNK][dimp]
-    float* vs = ks + SR_CHUNK * dimp;             // [SR_CHUNK][cpb]
+    const int row_f = SEG << log_split;           // floats of a staged token's q (or k)
+    float* qs = sm;                               // [SR_CHUNK][split][SEG]
+    float* ks = qs + SR_CHUNK * row_f;            // [SR_CHUNK][split][SEG]
+    float* vs = ks + SR_CHUNK * row_f;            // [SR_CHUNK][cpb]
     float* gb = vs + SR_CHUNK * cpb;              // [2][SR_CHUNK]: g, beta
-    const int e = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int e = e0 + blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int part = tid & (split - 1), col_l = tid >> log_split, c = blockIdx.z * cpb + col_l;
     const int q0 = qstart[e], n = qstart[e + 1] - q0;
     if (n <= 0) return;
@@ -258,12 +276,20 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     const int d0 = part * DPT;
     float S[DPT];
     {
-        const float* rd = state + (size_t)read_slots[e] * slot_stride + (size_t)h * dim * vdim;
+        const float* rd = state + (size_t)read_slots[e] * slot_stride + ((size_t)h * vdim + c) * dim;
+        if (live && (dim & 3) == 0) {             // a column's rows lie together: 16 bytes a load (dim a multiple of 4 keeps them aligned)
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) S[i] = (live && d0 + i < dim) ? rd[(size_t)(d0 + i) * vdim + c] : 0.f;
+            for (int i = 0; i < DPT; i += 4) {
+                const float4 x = d0 + i < dim ? *reinterpret_cast<const float4*>(rd + d0 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                S[i] = x.x, S[i + 1] = x.y, S[i + 2] = x.z, S[i + 3] = x.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) S[i] = (live && d0 + i < dim) ? rd[d0 + i] : 0.f;
+        }
     }
     const float dec = MODE == 0 ? decay[h] : 0.f;
-    constexpr int NQ = SR_CHUNK * DPT * 8 / SR_THREADS;    // staged q (and k) values per thread at the widest split (8)
+    constexpr int NQ = (SR_CHUNK * DPT * SR_MAX_SPLIT + SR_THREADS - 1) / SR_THREADS;    // staged q (and k) values per thread at the widest split
     constexpr int NV = SR_CHUNK;                           // staged v values per thread at split 1
     float qr[NQ], kr[NQ], vr[NV], gr = 0.f;
     const int n_qk = SR_CHUNK << log_dimp, n_v = SR_CHUNK << log_cpb;
@@ -295,14 +321,16 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
         for (int j = 0; j < NQ; ++j) {
             const int idx = tid + j * SR_THREADS;
             if (idx < n_qk) {
-                qs[idx] = in_act ? sm_silu(qr[j]) : qr[j];
-                ks[idx] = in_act ? sm_silu(kr[j]) : kr[j];
+                const int tt = idx >> log_dimp, d = idx & (dimp - 1);
+                const int at = tt * row_f + (d >> LOG_DPT) * SEG + (d & (DPT - 1));
+                qs[at] = in_act ? sm_silu_fast(qr[j]) : qr[j];
+                ks[at] = in_act ? sm_silu_fast(kr[j]) : kr[j];
             }
         }
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const int idx = tid + j * SR_THREADS;
-            if (idx < n_v) vs[idx] = in_act ? sm_silu(vr[j]) : vr[j];
+            if (idx < n_v) vs[idx] = in_act ? sm_silu_fast(vr[j]) : vr[j];
         }
         if (MODE == 1 && tid < 2 * SR_CHUNK) gb[tid] = gr;
     };
@@ -310,119 +338,169 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     fetch(0);
     stage();
     __syncthreads();
+    // The tokens of a chunk are unrolled (a token beyond the entry's end is skipped by a predicate), so that the loads of
+    // a later token's q and k are issued while an earlier token's products run; and a token's output is only summed over
+    // the lanes of its column when the chunk is done: its shuffles then wait for one another's results, not the tokens.
     for (int t0 = 0; t0 < n; t0 += SR_CHUNK) {
         const int nt = min(SR_CHUNK, n - t0);
         if (t0 + SR_CHUNK < n) fetch(t0 + SR_CHUNK);
-        for (int tt = 0; tt < nt; ++tt) {
-            const float4* qq = reinterpret_cast<const float4*>(qs + (tt << log_dimp) + d0);
-            const float4* kk = reinterpret_cast<const float4*>(ks + (tt << log_dimp) + d0);
-            const float vc = vs[(tt << log_cpb) + col_l];
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-            if (MODE == 0) {
+        float oacc[SR_CHUNK];
 #pragma unroll
-                for (int i = 0; i < DPT / 4; ++i) {
-                    const float4 k4 = kk[i], q4 = qq[i];
-                    S[4 * i] = fmaf(dec, S[4 * i], k4.x * vc);
-                    S[4 * i + 1] = fmaf(dec, S[4 * i + 1], k4.y * vc);
-                    S[4 * i + 2] = fmaf(dec, S[4 * i + 2], k4.z * vc);
-                    S[4 * i + 3] = fmaf(dec, S[4 * i + 3], k4.w * vc);
-                    o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
-                    o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
-                }
-            } else {
-                const float g = gb[tt], bt = gb[SR_CHUNK + tt];
-                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        for (int tt = 0; tt < SR_CHUNK; ++tt) {
+            oacc[tt] = 0.f;
+            if (tt < nt) {
+                const float4* qq = reinterpret_cast<const float4*>(qs + tt * row_f + part * SEG);
+                const float4* kk = reinterpret_cast<const float4*>(ks + tt * row_f + part * SEG);
+                const float vc = vs[(tt << log_cpb) + col_l];
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+                if (MODE == 0) {
 #pragma unroll
-                for (int i = 0; i < DPT / 4; ++i) {
-                    const float4 k4 = kk[i];
-                    S[4 * i] *= g, S[4 * i + 1] *= g, S[4 * i + 2] *= g, S[4 * i + 3] *= g;
-                    s0 = fmaf(S[4 * i], k4.x, s0), s1 = fmaf(S[4 * i + 1], k4.y, s1);
-                    s2 = fmaf(S[4 * i + 2], k4.z, s2), s3 = fmaf(S[4 * i + 3], k4.w, s3);
-                }
-                float sk = (s0 + s1) + (s2 + s3);
-                for (int m = split >> 1; m > 0; m >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, m);
-                const float u = bt * (vc - sk);
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        const float4 k4 = kk[i], q4 = qq[i];
+                        S[4 * i] = fmaf(dec, S[4 * i], k4.x * vc);
+                        S[4 * i + 1] = fmaf(dec, S[4 * i + 1], k4.y * vc);
+                        S[4 * i + 2] = fmaf(dec, S[4 * i + 2], k4.z * vc);
+                        S[4 * i + 3] = fmaf(dec, S[4 * i + 3], k4.w * vc);
+                        o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                        o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                    }
+                } else {
+                    const float g = gb[tt], bt = gb[SR_CHUNK + tt];
+                    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-                for (int i = 0; i < DPT / 4; ++i) {
-                    const float4 k4 = kk[i], q4 = qq[i];
-                    S[4 * i] = fmaf(k4.x, u, S[4 * i]);
-                    S[4 * i + 1] = fmaf(k4.y, u, S[4 * i + 1]);
-                    S[4 * i + 2] = fmaf(k4.z, u, S[4 * i + 2]);
-                    S[4 * i + 3] = fmaf(k4.w, u, S[4 * i + 3]);
-                    o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
-                    o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        const float4 k4 = kk[i];
+                        S[4 * i] *= g, S[4 * i + 1] *= g, S[4 * i + 2] *= g, S[4 * i + 3] *= g;
+                        s0 = fmaf(S[4 * i], k4.x, s0), s1 = fmaf(S[4 * i + 1], k4.y, s1);
+                        s2 = fmaf(S[4 * i + 2], k4.z, s2), s3 = fmaf(S[4 * i + 3], k4.w, s3);
+                    }
+                    float sk = (s0 + s1) + (s2 + s3);
+#pragma unroll
+                    for (int m = SR_MAX_SPLIT / 2; m > 0; m >>= 1)
+                        if (m < split) sk += __shfl_xor_sync(0xffffffffu, sk, m);
+                    const float u = bt * (vc - sk);
+#pragma unroll
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        const float4 k4 = kk[i], q4 = qq[i];
+                        S[4 * i] = fmaf(k4.x, u, S[4 * i]);
+                        S[4 * i + 1] = fmaf(k4.y, u, S[4 * i + 1]);
+                        S[4 * i + 2] = fmaf(k4.z, u, S[4 * i + 2]);
+                        S[4 * i + 3] = fmaf(k4.w, u, S[4 * i + 3]);
+                        o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                        o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                    }
                 }
+                oacc[tt] = (o0 + o1) + (o2 + o3);
             }
-            float o = (o0 + o1) + (o2 + o3);
-            for (int m = split >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-            if (live && part == 0) out[(size_t)(q0 + t0 + tt) * ldo + h * vdim + c] = o;
+        }
+#pragma unroll
+        for (int m = SR_MAX_SPLIT / 2; m > 0; m >>= 1)
+            if (m < split) {
+#pragma unroll
+                for (int tt = 0; tt < SR_CHUNK; ++tt) oacc[tt] += __shfl_xor_sync(0xffffffffu, oacc[tt], m);
+            }
+        if (live && part == 0) {
+#pragma unroll
+            for (int tt = 0; tt < SR_CHUNK; ++tt)
+                if (tt < nt) out[(size_t)(q0 + t0 + tt) * ldo + h * vdim + c] = oacc[tt];
         }
         __syncthreads();                          // everyone has read this chunk
         if (t0 + SR_CHUNK < n) stage();
         __syncthreads();
     }
     if (live) {
-        float* wr = state + (size_t)write_slots[e] * slot_stride + (size_t)h * dim * vdim;
+        float* wr = state + (size_t)write_slots[e] * slot_stride + ((size_t)h * vdim + c) * dim;
+        if ((dim & 3) == 0) {
 #pragma unroll
-        for (int i = 0; i < DPT; ++i)
-            if (d0 + i < dim) wr[(size_t)(d0 + i) * vdim + c] = S[i];
+            for (int i = 0; i < DPT; i += 4)
+                if (d0 + i < dim) *reinterpret_cast<float4*>(wr + d0 + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < DPT; ++i)
+                if (d0 + i < dim) wr[d0 + i] = S[i];
+        }
     }
 }
 
-template <int MODE, int DPT>
+template <int MODE, int DPT, int CH>
 static void sr_launch(dim3 grid, size_t smem, cudaStream_t stream, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v,
                       int H, int G, int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
-                      size_t slot_stride, const int* read_slots, const int* write_slots, const int* qstart, float* out, int ldo, int log_split) {
-    matrix_state_scan_reg_kernel<MODE, DPT><<<grid, SR_THREADS, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec,
-                                                                                state, slot_stride, read_slots, write_slots, qstart, out, ldo,
-                                                                                log_split);
+                      size_t slot_stride, const int* read_slots, const int* write_slots, const int* qstart, float* out, int ldo, int log_split,
+                      int e0) {
+    matrix_state_scan_reg_kernel<MODE, DPT, CH><<<grid, SR_THREADS, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta,
+                                                                                    gdec, state, slot_stride, read_slots, write_slots, qstart, out,
+                                                                                    ldo, log_split, e0);
+}
+
+// In place: x[t, c] = silu(x[t, c]) for the first `cols` columns of float32 rows (the recurrences' inputs, as a pass of its own).
+__global__ void silu_cols_kernel(float* x, int ld, int cols, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / cols;
+        float* p = x + t * ld + (idx - t * cols);
+        *p = sm_silu_fast(*p);
+    }
+}
+
+IL_EXPORT int il_silu_cols(float* x, int ld, int cols, int T, cudaStream_t stream) {
+    if (T <= 0 || cols <= 0) return IL_OK;
+    const size_t total = (size_t)T * cols;
+    silu_cols_kernel<<<sm_grid(total, 256), 256, 0, stream>>>(x, ld, cols, total);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
 }
 
 IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v, int H, int G,
                                    int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
                                    long long slot_stride, const int* read_slots, const int* write_slots, const int* qstart, int E,
-                                   float* out, int ldo, int generic, cudaStream_t stream) {
+                                   float* out, int ldo, int generic, int e0, int single, cudaStream_t stream) {
     if (E <= 0) return IL_OK;
+    if (e0 < 0) return IL_BAD_ARG;
     if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1)) return IL_BAD_ARG;
     if (mode == 0 ? !decay : (!beta || !gdec)) return IL_BAD_ARG;
     if (dim <= 256 && !generic) {
-        // rows of a column per lane (8, 16 or 32) and lanes per column (a power of two up to 8) that cover dim
-        const int dpt = dim <= 32 ? 8 : dim <= 128 ? 16 : 32;
+        // Rows of a column per lane (8 or 16) and lanes per column (a power of two up to 16) that cover dim. Few blocks (one
+        // long prompt) of the decayed sum take the narrower lanes: twice the warps, each with half the products per token
+        // (measured at 16 heads of 128 x 128 over 2,048 tokens: 945 -> 695 us); the delta rule, whose sum over the lanes
+        // stands between a token's two updates, loses by the longer shuffle chain (648 -> 771 us) and keeps 16.
+        int dpt = dim <= 32 ? 8 : 16;
+        if (mode == 0 && dim > 32 && dim <= 128) {
+            const int cols16 = SR_THREADS / ((dim + 15) / 16 <= 1 ? 1 : (dim <= 32 ? 2 : dim <= 64 ? 4 : 8));
+            if ((long long)E * H * ((vdim + cols16 - 1) / cols16) < 2 * 148) dpt = 8;
+        }
         int log_split = 0;
         while ((dpt << log_split) < dim) ++log_split;
-        const int dimp = dpt << log_split, cpb = SR_THREADS >> log_split;
-        const size_t smem_r = ((size_t)SR_CHUNK * (2 * dimp + cpb) + 2 * SR_CHUNK) * sizeof(float);
+        const int cpb = SR_THREADS >> log_split;
+        const int ch = single ? 1 : 8;
+        const size_t smem_r = ((size_t)ch * (2 * ((dpt + 4) << log_split) + cpb) + 2 * ch) * sizeof(float);
         const dim3 grid_r(E, H, (vdim + cpb - 1) / cpb);
 #define SR_ARGS grid_r, smem_r, stream, q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state, (size_t)slot_stride, \
-                read_slots, write_slots, qstart, out, ldo, log_split
+                read_slots, write_slots, qstart, out, ldo, log_split, e0
         if (mode == 0) {
-            if (dpt == 8) sr_launch<0, 8>(SR_ARGS);
-            else if (dpt == 16) sr_launch<0, 16>(SR_ARGS);
-            else sr_launch<0, 32>(SR_ARGS);
+            if (dpt == 8) { if (single) sr_launch<0, 8, 1>(SR_ARGS); else sr_launch<0, 8, 8>(SR_ARGS); }
+            else { if (single) sr_launch<0, 16, 1>(SR_ARGS); else sr_launch<0, 16, 8>(SR_ARGS); }
         } else {
-            if (dpt == 8) sr_launch<1, 8>(SR_ARGS);
-            else if (dpt == 16) sr_launch<1, 16>(SR_ARGS);
-            else sr_launch<1, 32>(SR_ARGS);
+            if (dpt == 8) { if (single) sr_launch<1, 8, 1>(SR_ARGS); else sr_launch<1, 8, 8>(SR_ARGS); }
+            else { if (single) sr_launch<1, 16, 1>(SR_ARGS); else sr_launch<1, 16, 8>(SR_ARGS); }
         }
         IL_LAUNCH_CHECK();
         return IL_OK;
     }
     int ncol = vdim >= 128 ? 128 : vdim > 32 ? 64 : 32;
-    size_t smem = ((size_t)dim * ncol + 2 * SM_CHUNK * dim) * sizeof(float);
+    size_t smem = ((size_t)dim * (ncol + 1) + 2 * SM_CHUNK * dim) * sizeof(float);
     while (smem > 200 * 1024 && ncol > 32) {
         ncol >>= 1;
-        smem = ((size_t)dim * ncol + 2 * SM_CHUNK * dim) * sizeof(float);
+        smem = ((size_t)dim * (ncol + 1) + 2 * SM_CHUNK * dim) * sizeof(float);
     }
     if (smem > 200 * 1024) return IL_UNSUPPORTED;
     const dim3 grid(E, H, (vdim + ncol - 1) / ncol);
     if (mode == 0) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         matrix_state_scan_kernel<0><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
-                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo);
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         matrix_state_scan_kernel<1><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
-                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo);
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0);
     }
     IL_LAUNCH_CHECK();
     return IL_OK;

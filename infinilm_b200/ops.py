@@ -1039,28 +1039,49 @@ SCAN_DECAY, SCAN_DELTA = 0, 1
 def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n_qk_heads: int, dim: int,
                       vdim: int, in_act: int, decay: Optional[torch.Tensor], beta: Optional[torch.Tensor],
                       gdec: Optional[torch.Tensor], state: torch.Tensor, read_slots: torch.Tensor, write_slots: torch.Tensor,
-                      entry_qstart: torch.Tensor, n_entries: int, out: torch.Tensor, generic: bool = False) -> None:
+                      entry_qstart: torch.Tensor, n_entries: int, out: torch.Tensor, generic: bool = False, first_entry: int = 0,
+                      single: bool = False) -> None:
     """A recurrence over a float32 state S [dim, vdim] per (request, head), token by token in each entry's order.
     SCAN_DECAY: S = decay[h] S + k v^T, o = S^T q. SCAN_DELTA: S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q.
     q, k float32 [T, >= n_qk_heads*dim] (views with a row stride), v float32 [T, >= n_heads*vdim], out float32 [T, n_heads*vdim];
     value head h reads q/k head h // (n_heads // n_qk_heads). in_act 1: silu on q, k, v as read.
-    state float32 [slots, n_heads, dim, vdim]. `generic`: the kernel that keeps the state in shared memory (any size; the
-    one that runs beyond a key size of 256) instead of the one that keeps it in registers."""
+    state float32 [slots, n_heads, vdim, dim] (S column by column: the dim entries behind one output lie together). `generic`: the kernel that keeps the state in shared memory (any size; the
+    one that runs beyond a key size of 256) instead of the one that keeps it in registers. Entries first_entry ..
+    first_entry + n_entries - 1 are run; `single`: each of them brings one token (the form made for decoding)."""
     _need_cuda(q, k, v, decay, beta, gdec, state, read_slots, write_slots, entry_qstart, out)
     _i32("matrix_state_scan", read_slots, write_slots, entry_qstart)
     for t in (q, k, v, out, state):
         if t.dtype != torch.float32 or t.stride(-1) != 1:
             raise KernelError("matrix_state_scan: float32 tensors with contiguous rows")
-    if not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, vdim):
-        raise KernelError("matrix_state_scan: state float32 [slots, heads, dim, vdim]")
+    if not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, vdim, dim):
+        raise KernelError("matrix_state_scan: state float32 [slots, heads, vdim, dim]")
     if out.shape[1] != n_heads * vdim or q.shape[1] < n_qk_heads * dim or k.shape[1] < n_qk_heads * dim or v.shape[1] < n_heads * vdim:
         raise KernelError("matrix_state_scan: shapes")
     f = _fn("seqmix", "il_matrix_state_scan", [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p,
-                                               _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+                                               _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), n_heads, n_qk_heads, dim, vdim, in_act,
              _ptr(decay), _ptr(beta), _ptr(gdec), _ptr(state), state.stride(0), _ptr(read_slots), _ptr(write_slots),
-             _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), int(generic), _stream()), "matrix_state_scan")
+             _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), int(generic), first_entry, int(single), _stream()), "matrix_state_scan")
+
+
+def matrix_state_scan_step(ctx, *args, **kw) -> None:
+    """`matrix_state_scan` over a step's entries: the single tokens (the first `ctx.n_decode` entries) by the form made for
+    them, the prompt portions behind them by the chunked form."""
+    n_dec, E = ctx.n_decode, ctx.n_entries
+    if n_dec > 0:
+        matrix_state_scan(*args, n_entries=n_dec, first_entry=0, single=True, **kw)
+    if E > n_dec:
+        matrix_state_scan(*args, n_entries=E - n_dec, first_entry=n_dec, single=False, **kw)
+
+
+def silu_cols(x: torch.Tensor, cols: int) -> None:
+    """x[:, :cols] = silu(x[:, :cols]) in place, float32 rows (the same SiLU the recurrence kernels apply to their inputs)."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1 or cols > x.shape[1]:
+        raise KernelError("silu_cols: float32 [T, >= cols] with contiguous rows")
+    f = _fn("seqmix", "il_silu_cols", [_c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), cols, x.shape[0], _stream()), "silu_cols")
 
 
 GATE_SIGMOID, GATE_SILU = 0, 1

@@ -28,6 +28,7 @@ class DecayLinearAttention(Mixer):
     """params: hidden, n_heads, qk_dim, v_dim, decay (one number per head), eps (of the output norm).
     Tensors: q, k, v, g, o [out, in]; norm [heads * v_dim]."""
     graph_safe = True
+    ACT_PASS_ROWS = 64
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
@@ -54,15 +55,19 @@ class DecayLinearAttention(Mixer):
         self.decay = torch.tensor(self.decay_list, dtype=torch.float64).to(torch.float32).to(t["q"].device)
 
     def cache_need(self):
-        return CacheNeed("state", shape=(self.nh, self.dk, self.dv), dtype="float32")
+        return CacheNeed("state", shape=(self.nh, self.dv, self.dk), dtype="float32")
 
     def forward(self, x, ctx, cache):
         T, nqk, nv = x.shape[0], self.nqk, self.nv
         proj = self.proj(x, ctx.ws.rows("dla_proj", T, 2 * nqk + 2 * nv, torch.float32), out_f32=True)
         o = ctx.ws.rows("dla_o", T, nv, torch.float32)
-        ops.matrix_state_scan(ops.SCAN_DECAY, proj[:, :nqk], proj[:, nqk: 2 * nqk], proj[:, 2 * nqk: 2 * nqk + nv], self.nh, self.nh,
-                              self.dk, self.dv, 1, self.decay, None, None, cache.storage, cache.read_slots,
-                              cache.write_slots if cache.writable else cache.read_slots, ctx.entry_qstart, ctx.n_entries, o)
+        in_act = 1
+        if T > self.ACT_PASS_ROWS:                # many rows: the activation as a pass of its own (the same function), not in the token loop
+            ops.silu_cols(proj, 2 * nqk + nv)
+            in_act = 0
+        ops.matrix_state_scan_step(ctx, ops.SCAN_DECAY, proj[:, :nqk], proj[:, nqk: 2 * nqk], proj[:, 2 * nqk: 2 * nqk + nv], self.nh, self.nh,
+                                   self.dk, self.dv, in_act, self.decay, None, None, cache.storage, cache.read_slots,
+                                   cache.write_slots if cache.writable else cache.read_slots, ctx.entry_qstart, out=o)
         gated = ctx.ws.rows("dla_gated", T, nv, self.dtype)
         ops.group_norm_gate(o, self.norm_w, self.eps, proj, 2 * nqk + nv, ops.GATE_SIGMOID, gated, nv)
         return self.o_proj(gated, ctx.ws.rows("dla_branch", T, self.hidden, self.dtype))
@@ -117,7 +122,7 @@ class GatedDeltaRule(Mixer):
         self.norm_w = t["norm"].contiguous()
 
     def cache_need(self):
-        return (CacheNeed("state", shape=(self.nh, self.dk, self.dv), dtype="float32"), self.conv.state_need())
+        return (CacheNeed("state", shape=(self.nh, self.dv, self.dk), dtype="float32"), self.conv.state_need())
 
     def forward(self, x, ctx, cache):
         S, conv_state = cache
@@ -130,9 +135,9 @@ class GatedDeltaRule(Mixer):
         ops.delta_prep(qkv, 0, nqk, self.ng, self.dk, self.dk ** -0.5, self.unit_eps, proj, self.n_conv, self.n_conv + nh,
                        self.a_log, self.dt_bias, beta, gdec, nh)
         o = ctx.ws.rows("gdr_o", T, nv, torch.float32)
-        ops.matrix_state_scan(ops.SCAN_DELTA, qkv[:, :nqk], qkv[:, nqk: 2 * nqk], qkv[:, 2 * nqk:], nh, self.ng, self.dk, self.dv, 0,
-                              None, beta, gdec, S.storage, S.read_slots, S.write_slots if S.writable else S.read_slots,
-                              ctx.entry_qstart, ctx.n_entries, o)
+        ops.matrix_state_scan_step(ctx, ops.SCAN_DELTA, qkv[:, :nqk], qkv[:, nqk: 2 * nqk], qkv[:, 2 * nqk:], nh, self.ng, self.dk, self.dv, 0,
+                                   None, beta, gdec, S.storage, S.read_slots, S.write_slots if S.writable else S.read_slots,
+                                   ctx.entry_qstart, out=o)
         gated = ctx.ws.rows("gdr_gated", T, nv, self.dtype)
         ops.group_norm_gate(o, self.norm_w, self.eps, proj, self.n_conv + 2 * nh, ops.GATE_SILU, gated, self.dv)
         return self.o_proj(gated, ctx.ws.rows("gdr_branch", T, self.hidden, self.dtype))

@@ -80,7 +80,7 @@ def _scan(ops, mode, q, k, v, H, G, d, dv, decay, beta, g, state, slot, first, d
     qstart, _ = _step_arrays([n], dev)
     out = torch.empty(n, H * dv, device=dev)
     ops.matrix_state_scan(mode, q, k, v, H, G, d, dv, act, decay, beta, g, state, _i32([0 if first else slot], dev), _i32([slot], dev),
-                          qstart, 1, out, generic=GENERIC)
+                          qstart, 1, out, generic=GENERIC, single=(n == 1))
     return out
 
 
@@ -95,7 +95,7 @@ def test_decayed_sum_whole_and_token_by_token(cuda_device, scan_kernel, H, G, d,
     rep = H // G
     want = P.decayed_linear_attention(P.silu(q.double()).view(T, G, d).repeat_interleave(rep, 1), P.silu(k.double()).view(T, G, d).repeat_interleave(rep, 1),
                                       P.silu(v.double()).view(T, H, dv), decay.double()).reshape(T, H * dv)
-    state = torch.zeros(4, H, d, dv, device=dev)
+    state = torch.zeros(4, H, dv, d, device=dev)
     state[2] = 3.0
     qd, kd, vd, dd = q.to(dev), k.to(dev), v.to(dev), decay.to(dev)
     whole = _scan(ops, ops.SCAN_DECAY, qd, kd, vd, H, G, d, dv, dd, None, None, state, 1, True, dev, act=1)
@@ -136,7 +136,7 @@ def test_delta_rule_with_its_preparation(cuda_device, scan_kernel, H, G, d, dv):
     ops.delta_prep(qkd, 0, G * d, G, d, d ** -0.5, 1e-6, abd, 1, 1 + H, a_log.to(dev), dt_bias.to(dev), b_dev, g_dev, H)
     assert float((b_dev.cpu().double() - beta).abs().max()) < 1e-6 and float((g_dev.cpu().double() - g).abs().max()) < 1e-6
     assert float((qkd[:, :G * d].cpu().double().view(T, G, d) - qn).abs().max()) < 1e-6
-    state = torch.zeros(3, H, d, dv, device=dev)
+    state = torch.zeros(3, H, dv, d, device=dev)
     vd = v.to(dev)
     whole = _scan(ops, ops.SCAN_DELTA, qkd[:, :G * d], qkd[:, G * d:], vd, H, G, d, dv, None, b_dev, g_dev, state, 1, True, dev)
     scale = float(want.abs().max())
@@ -157,7 +157,7 @@ def test_scan_of_a_batch_equals_each_alone(cuda_device, scan_kernel):
     T = sum(lens)
     q, k, v = (torch.randn(T, H * n, device=dev) for n in (d, d, dv))
     decay = torch.tensor([0.9, 0.99], device=dev)
-    state = torch.randn(6, H, d, dv, device=dev)
+    state = torch.randn(6, H, dv, d, device=dev)
     state[0] = 0
     before = state.clone()
     qstart, _ = _step_arrays(lens, dev)
@@ -171,6 +171,21 @@ def test_scan_of_a_batch_equals_each_alone(cuda_device, scan_kernel):
         assert torch.equal(one, out[a:a + n]) and torch.equal(st[int(wr[e])], state[int(wr[e])])
         a += n
     assert torch.equal(state[5], before[5]) and float(state[0].abs().max()) == 0.0
+    # as a step runs it: single tokens first, by the form made for them, the portions behind them by the chunked form
+    lens2 = [1, 1, 5, 40]
+    T2 = sum(lens2)
+    qs2, _ = _step_arrays(lens2, dev)
+    st2, out2 = before.clone(), torch.empty(T2, H * dv, device=dev)
+
+    class Ctx:
+        n_decode, n_entries = 2, 4
+    ops.matrix_state_scan_step(Ctx, ops.SCAN_DECAY, q[:T2], k[:T2], v[:T2], H, H, d, dv, 0, decay, None, None, st2, rd, wr, qs2, out=out2, generic=GENERIC)
+    a = 0
+    for e, n in enumerate(lens2):
+        st = before.clone()
+        one = _scan(ops, ops.SCAN_DECAY, q[a:a + n], k[a:a + n], v[a:a + n], H, H, d, dv, decay, None, None, st, int(wr[e]), int(rd[e]) == 0, dev)
+        assert torch.equal(one, out2[a:a + n]) and torch.equal(st[int(wr[e])], st2[int(wr[e])])
+        a += n
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
