@@ -249,8 +249,7 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
 // chunk's values are loaded into registers while the current chunk is computed, so the token loop waits for no global
 // load. Per token the critical path is one multiply, one dot product of DPT terms, log2(split) shuffles and one update.
 #define SR_THREADS 128
-#define SR_MAX_SPLIT 16
-template <int MODE, int DPT, int SR_CHUNK>
+template <int MODE, int DPT, int SR_CHUNK, int SR_MAX_SPLIT>
 __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld_q, int ld_k, int ld_v, int H, int G,
     int dim, int vdim, int in_act, const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
@@ -365,12 +364,13 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
                         o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
                     }
                 } else {
+                    // g scales the whole state, so S^T k of the scaled state is g times that of the old one, and the
+                    // scaling joins the update as one fused multiply-add: S = g S + k u
                     const float g = gb[tt], bt = gb[SR_CHUNK + tt];
                     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
                     for (int i = 0; i < DPT / 4; ++i) {
                         const float4 k4 = kk[i];
-                        S[4 * i] *= g, S[4 * i + 1] *= g, S[4 * i + 2] *= g, S[4 * i + 3] *= g;
                         s0 = fmaf(S[4 * i], k4.x, s0), s1 = fmaf(S[4 * i + 1], k4.y, s1);
                         s2 = fmaf(S[4 * i + 2], k4.z, s2), s3 = fmaf(S[4 * i + 3], k4.w, s3);
                     }
@@ -378,14 +378,14 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
 #pragma unroll
                     for (int m = SR_MAX_SPLIT / 2; m > 0; m >>= 1)
                         if (m < split) sk += __shfl_xor_sync(0xffffffffu, sk, m);
-                    const float u = bt * (vc - sk);
+                    const float u = bt * (vc - g * sk);
 #pragma unroll
                     for (int i = 0; i < DPT / 4; ++i) {
                         const float4 k4 = kk[i], q4 = qq[i];
-                        S[4 * i] = fmaf(k4.x, u, S[4 * i]);
-                        S[4 * i + 1] = fmaf(k4.y, u, S[4 * i + 1]);
-                        S[4 * i + 2] = fmaf(k4.z, u, S[4 * i + 2]);
-                        S[4 * i + 3] = fmaf(k4.w, u, S[4 * i + 3]);
+                        S[4 * i] = fmaf(g, S[4 * i], k4.x * u);
+                        S[4 * i + 1] = fmaf(g, S[4 * i + 1], k4.y * u);
+                        S[4 * i + 2] = fmaf(g, S[4 * i + 2], k4.z * u);
+                        S[4 * i + 3] = fmaf(g, S[4 * i + 3], k4.w * u);
                         o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
                         o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
                     }
@@ -422,12 +422,12 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     }
 }
 
-template <int MODE, int DPT, int CH>
+template <int MODE, int DPT, int CH, int MS>
 static void sr_launch(dim3 grid, size_t smem, cudaStream_t stream, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v,
                       int H, int G, int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
                       size_t slot_stride, const int* read_slots, const int* write_slots, const int* qstart, float* out, int ldo, int log_split,
                       int e0) {
-    matrix_state_scan_reg_kernel<MODE, DPT, CH><<<grid, SR_THREADS, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta,
+    matrix_state_scan_reg_kernel<MODE, DPT, CH, MS><<<grid, SR_THREADS, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta,
                                                                                     gdec, state, slot_stride, read_slots, write_slots, qstart, out,
                                                                                     ldo, log_split, e0);
 }
@@ -475,12 +475,16 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
         const dim3 grid_r(E, H, (vdim + cpb - 1) / cpb);
 #define SR_ARGS grid_r, smem_r, stream, q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state, (size_t)slot_stride, \
                 read_slots, write_slots, qstart, out, ldo, log_split, e0
+        // (the widest split a variant is built for sizes its staging registers: 8 lanes up to dim = 8 DPT, 16 beyond)
+#define SR_PICK(MODE_, DPT_)                                                                                     \
+        do {                                                                                                     \
+            if (log_split <= 3) { if (single) sr_launch<MODE_, DPT_, 1, 8>(SR_ARGS); else sr_launch<MODE_, DPT_, 8, 8>(SR_ARGS); } \
+            else { if (single) sr_launch<MODE_, DPT_, 1, 16>(SR_ARGS); else sr_launch<MODE_, DPT_, 8, 16>(SR_ARGS); }               \
+        } while (0)
         if (mode == 0) {
-            if (dpt == 8) { if (single) sr_launch<0, 8, 1>(SR_ARGS); else sr_launch<0, 8, 8>(SR_ARGS); }
-            else { if (single) sr_launch<0, 16, 1>(SR_ARGS); else sr_launch<0, 16, 8>(SR_ARGS); }
+            if (dpt == 8) SR_PICK(0, 8); else SR_PICK(0, 16);
         } else {
-            if (dpt == 8) { if (single) sr_launch<1, 8, 1>(SR_ARGS); else sr_launch<1, 8, 8>(SR_ARGS); }
-            else { if (single) sr_launch<1, 16, 1>(SR_ARGS); else sr_launch<1, 16, 8>(SR_ARGS); }
+            if (dpt == 8) SR_PICK(1, 8); else SR_PICK(1, 16);
         }
         IL_LAUNCH_CHECK();
         return IL_OK;
