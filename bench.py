@@ -327,7 +327,9 @@ class OpTimer:
             e1.record()
             lab = label or name
             if lab == "matrix_state_scan":
-                lab += " delta" if a[0] == 1 else " decay"
+                lab += (" delta" if a[0] == 1 else " decay") + (" single" if k.get("single") else "")
+            elif lab == "short_conv":
+                lab += f"[{a[10]}x{a[11]}]"
             if lab == "linear":
                 x = a[1] if len(a) > 1 else k["x"]
                 lab = f"linear[{a[0].out_features}x{a[0].in_features}]" + ("" if x.shape[0] > 16 else " skinny")
@@ -347,7 +349,7 @@ class OpTimer:
         for name in ("embed", "embed_pair_pos", "add_rmsnorm", "swiglu", "rope_store", "attention_plain", "attention_decode",
                      "attention_prefill", "attention_prefill_tc5", "gemm_skinny", "gemm_skinny_resid", "gemm_skinny_rope", "gemm_mid",
                      "gemm_tc5", "latent_norm_store", "moe_route", "moe_sort", "moe_combine", "gather_rows", "gemm_grouped", "short_conv",
-                     "short_conv_state", "delta_prep", "matrix_state_scan", "group_norm_gate", "head_gate", "scaled_sum", "softcap"):
+                     "short_conv_state", "delta_prep", "matrix_state_scan", "group_norm_gate", "head_gate", "scaled_sum", "softcap", "silu_cols"):
             self._wrap(ops, name)
         self._wrap(Linear, "__call__", "linear")
         if hasattr(F, "grouped_mm"):

@@ -465,7 +465,7 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
         int dpt = dim <= 32 ? 8 : 16;
         if (mode == 0 && dim > 32 && dim <= 128) {
             const int cols16 = SR_THREADS / ((dim + 15) / 16 <= 1 ? 1 : (dim <= 32 ? 2 : dim <= 64 ? 4 : 8));
-            if ((long long)E * H * ((vdim + cols16 - 1) / cols16) < 2 * 148) dpt = 8;
+            if ((long long)E * H * ((vdim + cols16 - 1) / cols16) <= 148) dpt = 8;     // at most one block an SM otherwise
         }
         int log_split = 0;
         while ((dpt << log_split) < dim) ++log_split;
