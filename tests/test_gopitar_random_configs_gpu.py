@@ -1,0 +1,76 @@
+"""Gopitar at sizes drawn from a seed: widths that are no multiple of 8, key and value sizes with and without a fast
+attention kernel and unequal in either direction, one head or many, grouped or not, windows from 1 to beyond the sequence,
+1 to 6 taps or no convolution, rotation over none, part or all of a head, any number of linear and delta heads, layers
+without a feed-forward, any order of layers, loops anywhere and none. Each configuration runs a prompt whole, in portions
+and token by token against the plain implementation, in both dtypes."""
+import random
+import warnings
+
+import pytest
+import torch
+
+import plain_gopitar as P
+from gopitar_configs import _delta, _left, _parallel, make_weights, token_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def random_config(seed: int) -> dict:
+    rng = random.Random(1000 + seed)
+    width = rng.choice([40, 72, 100, 136, 200, 264])
+    n_layers = rng.randint(1, 4)
+    layers = []
+    for _ in range(n_layers):
+        ff = rng.choice([None, 24, 56, 100]) if rng.random() < 0.85 else None
+        if rng.random() < 0.6:
+            kv = rng.randint(1, 3)
+            dim = rng.choice([4, 8, 12, 16, 24, 40, 64, 96, 128])
+            rot = rng.choice([0, 2, dim // 2 // 2 * 2, dim // 2 * 2])
+            left = _left(kv * rng.randint(1, 3), kv, dim, rng.choice([4, 8, 20, 32, 64, 80, 128]), rng.randint(1, 6),
+                         rng.choice([1, 2, 5, 16, 17, 31, 32, 48, 1000]), rot, rng.choice([10.0, 10000.0, 500000.0]), round(rng.uniform(0.05, 0.4), 3))
+            if rng.random() < 0.15:
+                del left["conv"]
+            heads = rng.randint(1, 5)
+            layers.append(_parallel(left, heads, rng.choice([4, 8, 20, 32, 64]), rng.choice([4, 12, 32, 48, 72]),
+                                    [round(rng.choice([rng.uniform(0.3, 0.9), rng.uniform(0.95, 0.9995)]), 5) for _ in range(heads)],
+                                    round(rng.uniform(0.3, 1.3), 2), round(rng.uniform(0.3, 1.3), 2), ff))
+        else:
+            g = rng.randint(1, 3)
+            layers.append(_delta(g * rng.randint(1, 3), g, rng.choice([4, 8, 20, 32, 64, 128]), rng.choice([4, 12, 32, 48, 72, 128]), rng.randint(1, 6), ff))
+    raw = {"architecture": "Gopitar", "vocab": rng.choice([50, 129, 333]), "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])},
+           "embedding": {"scale": rng.choice([0.5, 1.0, 4.0, 11.0])}, "layers": layers}
+    if rng.random() < 0.7:
+        raw["logit_softcap"] = rng.choice([5.0, 15.0, 50.0])
+    if rng.random() < 0.75:
+        a = rng.randint(0, n_layers - 1)
+        raw["loop"] = {"start": a, "stop": rng.randint(a + 1, n_layers), "times": rng.randint(1, 3)}
+    return raw
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_random_configuration(cuda_device, seed, dtype):
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.engine import Engine, StepEntry
+    raw = random_config(seed)
+    w = make_weights(raw, seed)
+    ids = token_ids(75, raw["vocab"], seed)
+    ref = P.forward(raw, w, ids)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", RuntimeWarning)
+        eng = Engine.from_tensors(config_from_json(raw), w, dtype=dtype, page_size=16, num_pages=8, max_seqs=2, max_batch_tokens=128)
+    tol = 4e-5 if dtype == "float32" else 5e-2
+    for cuts in ([75], [33, 2, 17, 1, 1, 21], [16] + [1] * 59):
+        seq, outs, a = eng.open(str(cuts[0])), [], 0
+        for c in cuts:
+            outs.append(eng.step([StepEntry(seq, ids[a:a + c], list(range(c)))]).clone())
+            a += c
+        eng.close(seq)
+        got = torch.cat(outs, 0).double().cpu()
+        err = ((got - ref).abs() / ref.abs().amax(dim=-1, keepdim=True)).amax(dim=-1)
+        n_bad = int((err > tol).sum())
+        assert torch.isfinite(got).all()
+        assert n_bad <= (0 if dtype == "float32" else len(ids) // 25) and (dtype == "float32" or float(err.max()) <= 3 * tol), \
+            f"seed {seed} cuts {cuts[:3]}: {n_bad} positions over {tol:.0e}, worst {float(err.max()):.2e}; config {raw}"
+    eng.synchronize()
+    eng.cache.check_invariants()

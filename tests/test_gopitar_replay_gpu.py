@@ -99,13 +99,18 @@ def test_whole_prompts(cuda_device, name, seed, dtype):
     eng.cache.check_invariants()
 
 
+@pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,seed", CASES)
-def test_prompt_then_token_by_token(cuda_device, name, seed, dtype):
+def test_prompt_then_token_by_token(cuda_device, name, seed, dtype, graphs):
     """Prefill against decoding through the cache and the states: the last 60 tokens one by one (longer than every window
-    but one, so the window passes over decoded tokens); and a sequence decoded from its very first token on."""
+    but one, so the window passes over decoded tokens); and a sequence decoded from its very first token on. With `graphs`
+    the single-token steps are captured and replayed as CUDA graphs (padded to a bucket of entries)."""
     raw = GOPITAR[name]()
     eng = _engine(raw, make_weights(raw, seed), dtype)
+    if graphs:
+        eng.enable_graphs()
+        assert eng.model.graph_safe
     ids = token_ids(110, raw["vocab"], 7)
     _check(_run_cut(eng, ids, [50] + [1] * 60), _oracle(name, seed, ids), dtype, f"{name} 50 + 60 x 1")
     ids = token_ids(45, raw["vocab"], 8)
@@ -203,6 +208,20 @@ def test_greedy_generation_through_llm(cuda_device, dtype):
                 assert t == int(torch.argmax(lg)), f"token {len(ids) - len(p)}"
             ids.append(t)
     llm.close()
+
+
+def test_command_line_on_a_random_folder(cuda_device, tmp_path):
+    """The package's command line: write a folder of random weights for a configuration, then generate from it."""
+    from infinilm_b200 import cli
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(GOPITAR["a"]()))
+    folder = str(tmp_path / "m")
+    assert cli.main(["--write-random-model", folder, "--config", str(cfg_path), "--seed", "3"]) == 0
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", RuntimeWarning)
+        rc = cli.main(["--model", folder, "--enable-paged-attn", "--block-size", "16", "--num-blocks", "32", "--prompt-len", "21",
+                       "--max-new-tokens", "9", "--batch-size", "2", "--ignore-eos", "--enable-graph", "--log-level", "ERROR"])
+    assert rc == 0
 
 
 def test_trace_runner_as_a_process(cuda_device, tmp_path):
