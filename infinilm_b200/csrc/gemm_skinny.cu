@@ -172,13 +172,13 @@ static cudaError_t gs_launch(const void* x, int ldx, const void* W, int ldw, voi
 
 // glu = 1: W is [2N, K] (N gate rows, then N up rows), bias [2N], out[M,N] = silu(alpha*x.Wg^T + bg) * (alpha*x.Wu^T + bu);
 // glu = 2: the same with gelu_tanh in place of silu.
-// norm_partial (may be null; without glu: bfloat16 out): x is residual * norm weight and still wants its 1/rms, from these sums of squares
+// norm_partial (may be null): x is residual * norm weight and still wants its 1/rms, from these sums of squares
 // [M][n_partial] (n_partial <= 256, H = the width they were summed over).
 IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int out_kind, int ldo, const float* bias,
                              float alpha, int M, int N, int K, int glu, const float* norm_partial, int n_partial, int norm_h,
                              float norm_eps, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return IL_OK;
-    if (norm_partial && (n_partial <= 0 || n_partial > GS_NORM_MAX_PARTIALS || norm_h <= 0 || (!glu && out_kind != IL_BF16))) return IL_UNSUPPORTED;
+    if (norm_partial && (n_partial <= 0 || n_partial > GS_NORM_MAX_PARTIALS || norm_h <= 0)) return IL_UNSUPPORTED;
     const GsNormIn ni{norm_partial, n_partial, norm_partial ? 1.f / (float)norm_h : 0.f, norm_eps};
     if (M > 16 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K || ldo < N) return IL_UNSUPPORTED;
     if (out_kind != IL_F32 && out_kind != IL_BF16) return IL_BAD_ARG;
@@ -187,13 +187,15 @@ IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, voi
     if (M <= 8) {
         if (glu == 2) e = gs_launch<1, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (glu) e = gs_launch<1, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
-        else if (norm_partial) e = gs_launch<1, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (norm_partial && out_kind == IL_BF16) e = gs_launch<1, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (norm_partial) e = gs_launch<1, 0, float, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (out_kind == IL_BF16) e = gs_launch<1, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
         else e = gs_launch<1, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     } else {
         if (glu == 2) e = gs_launch<2, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (glu) e = gs_launch<2, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
-        else if (norm_partial) e = gs_launch<2, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (norm_partial && out_kind == IL_BF16) e = gs_launch<2, 0, __nv_bfloat16, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
+        else if (norm_partial) e = gs_launch<2, 0, float, true>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream, ni);
         else if (out_kind == IL_BF16) e = gs_launch<2, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
         else e = gs_launch<2, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     }

@@ -461,7 +461,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
                 bias: Optional[torch.Tensor] = None, glu: int = 0, norm_in: Optional[NormedInput] = None) -> None:
     """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) for M <= 16 bfloat16 rows; out bfloat16 or float32.
     glu (True, or ACT_SILU / ACT_GELU_TANH): w is [2N,K] (gate rows, then up rows) and out[M,N] = act(gate) * up.
-    norm_in (with glu, or with a bfloat16 out): x is `norm_in.xw`, and the results are divided by the rms that its sums give."""
+    norm_in: x is `norm_in.xw`, and the results are divided by the rms that its sums give."""
     _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0] // 2 if glu else w.shape[0]
@@ -471,8 +471,6 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
         raise KernelError("gemm_skinny: innermost dimension must be contiguous")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0]):
         raise KernelError("gemm_skinny: bias float32, one per weight row")
-    if norm_in is not None and not glu and out.dtype != torch.bfloat16:
-        raise KernelError("gemm_skinny: norm_in goes with glu=True or a bfloat16 out")
     f = _fn("gemm_skinny", "il_gemm_skinny", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
                                               _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_float,
                                               _c_void_p])

@@ -92,10 +92,22 @@ class ConvGatedAttention(Mixer):
     def cache_need(self):
         return (CacheNeed("paged_kv", n_kv_heads=self.nkv, head_dim=self.hd, window=self.window), self.conv.state_need())
 
-    def forward(self, x, ctx, cache):
+    # A decode step of a few bfloat16 rows: the first product may take rows whose norm is only half done (it divides by the
+    # rms itself) and the output product may add into the residual and prepare the next norm, as the framework's other mixers do.
+    def accepts_normed(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden)
+
+    def fuses_tail(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_resid_ok(T, self.nh * self.dv, self.hidden)
+
+    def forward(self, x, ctx, cache, tail=None):
         pages, state = cache
         T, hd = x.shape[0], self.hd
-        proj = self.proj(x, ctx.ws.rows("cga_proj", T, self.n_proj_pad, self.dtype))
+        proj = ctx.ws.rows("cga_proj", T, self.n_proj_pad, self.dtype)
+        if isinstance(x, ops.NormedInput):
+            ops.gemm_skinny(x.xw, self.proj.weight, proj, 1.0, self.proj.bias, norm_in=x)
+        else:
+            self.proj(x, proj)
         qkv = ctx.ws.rows("cga_qkv", T, (self.nh + 2 * self.nkv) * hd, self.dtype)
         # the convolution writes heads at the common size hd, the surplus columns zero
         self.conv.run(proj, 0, ctx, state, qkv, [(0, self.nh + self.nkv, self.dk, 0, hd),
@@ -112,6 +124,10 @@ class ConvGatedAttention(Mixer):
             else:
                 ops.head_gate(att, hd, None, 0, gated, self.nh, self.dv)
             att = gated
+        if tail is not None:
+            return ops.gemm_skinny_resid(att, self.o_proj.weight, self.o_proj.alpha, self.o_proj.bias, tail.resid, tail.scale,
+                                         tail.norm.weight, tail.norm.eps, ctx.ws.rows("xw_mixer", T, self.hidden, self.dtype),
+                                         ctx.ws.rows("sumsq_mixer", T, (self.hidden + 15) // 16, torch.float32))
         return self.o_proj(att, ctx.ws.rows("cga_branch", T, self.hidden, self.dtype))
 
 

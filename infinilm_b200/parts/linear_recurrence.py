@@ -24,7 +24,32 @@ from .short_conv import ShortConv
 from .spec import CacheNeed, WeightSpec
 
 
-class DecayLinearAttention(Mixer):
+class _FusableEnds:
+    """What both mixers of this file share at their two ends in a decode step of a few bfloat16 rows: the first product takes
+    rows whose norm is only half done (and leaves float32), the output product adds into the residual and prepares the next norm."""
+
+    def accepts_normed(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden)
+
+    def fuses_tail(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_resid_ok(T, self.nv, self.hidden)
+
+    def _project(self, x, out):
+        if isinstance(x, ops.NormedInput):
+            ops.gemm_skinny(x.xw, self.proj.weight, out, 1.0, None, norm_in=x)
+            return out
+        return self.proj(x, out, out_f32=True)
+
+    def _output(self, gated, ctx, tail, tag):
+        T = gated.shape[0]
+        if tail is not None:
+            return ops.gemm_skinny_resid(gated, self.o_proj.weight, self.o_proj.alpha, None, tail.resid, tail.scale, tail.norm.weight,
+                                         tail.norm.eps, ctx.ws.rows("xw_mixer", T, self.hidden, self.dtype),
+                                         ctx.ws.rows("sumsq_mixer", T, (self.hidden + 15) // 16, torch.float32))
+        return self.o_proj(gated, ctx.ws.rows(tag, T, self.hidden, self.dtype))
+
+
+class DecayLinearAttention(_FusableEnds, Mixer):
     """params: hidden, n_heads, qk_dim, v_dim, decay (one number per head), eps (of the output norm).
     Tensors: q, k, v, g, o [out, in]; norm [heads * v_dim]."""
     graph_safe = True
@@ -57,9 +82,9 @@ class DecayLinearAttention(Mixer):
     def cache_need(self):
         return CacheNeed("state", shape=(self.nh, self.dv, self.dk), dtype="float32")
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, tail=None):
         T, nqk, nv = x.shape[0], self.nqk, self.nv
-        proj = self.proj(x, ctx.ws.rows("dla_proj", T, 2 * nqk + 2 * nv, torch.float32), out_f32=True)
+        proj = self._project(x, ctx.ws.rows("dla_proj", T, 2 * nqk + 2 * nv, torch.float32))
         o = ctx.ws.rows("dla_o", T, nv, torch.float32)
         in_act = 1
         if T > self.ACT_PASS_ROWS:                # many rows: the activation as a pass of its own (the same function), not in the token loop
@@ -70,10 +95,10 @@ class DecayLinearAttention(Mixer):
                                    cache.write_slots if cache.writable else cache.read_slots, ctx.entry_qstart, out=o)
         gated = ctx.ws.rows("dla_gated", T, nv, self.dtype)
         ops.group_norm_gate(o, self.norm_w, self.eps, proj, 2 * nqk + nv, ops.GATE_SIGMOID, gated, nv)
-        return self.o_proj(gated, ctx.ws.rows("dla_branch", T, self.hidden, self.dtype))
+        return self._output(gated, ctx, tail, "dla_branch")
 
 
-class GatedDeltaRule(Mixer):
+class GatedDeltaRule(_FusableEnds, Mixer):
     """params: hidden, n_heads (value heads), n_qk_heads, qk_dim, v_dim, conv_taps, eps (of the output norm), unit_eps (inside
     the root that makes q and k unit vectors, default 1e-6).
     Tensors: q, k [n_qk_heads * qk_dim, in], v, g [n_heads * v_dim, in], b, a [n_heads, in], o; q.conv, k.conv, v.conv
@@ -124,10 +149,10 @@ class GatedDeltaRule(Mixer):
     def cache_need(self):
         return (CacheNeed("state", shape=(self.nh, self.dv, self.dk), dtype="float32"), self.conv.state_need())
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, tail=None):
         S, conv_state = cache
         T, nqk, nv, nh = x.shape[0], self.nqk, self.nv, self.nh
-        proj = self.proj(x, ctx.ws.rows("gdr_proj", T, self.n_proj_pad, torch.float32), out_f32=True)
+        proj = self._project(x, ctx.ws.rows("gdr_proj", T, self.n_proj_pad, torch.float32))
         qkv = ctx.ws.rows("gdr_qkv", T, self.n_conv, torch.float32)
         self.conv.run(proj, 0, ctx, conv_state, qkv, [(0, 1, self.n_conv, 0, self.n_conv)], act=1)
         beta = ctx.ws.rows("gdr_beta", T, nh, torch.float32)
@@ -140,7 +165,7 @@ class GatedDeltaRule(Mixer):
                                    ctx.entry_qstart, out=o)
         gated = ctx.ws.rows("gdr_gated", T, nv, self.dtype)
         ops.group_norm_gate(o, self.norm_w, self.eps, proj, self.n_conv + 2 * nh, ops.GATE_SILU, gated, self.dv)
-        return self.o_proj(gated, ctx.ws.rows("gdr_branch", T, self.hidden, self.dtype))
+        return self._output(gated, ctx, tail, "gdr_branch")
 
 
 register_part("mixer", "decay_linear_attention", DecayLinearAttention)

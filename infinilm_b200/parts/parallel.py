@@ -9,7 +9,7 @@ from typing import Dict, List
 import torch
 
 from .. import ops
-from .base import Mixer, build_part, register_part
+from .base import Mixer, ResidualTail, build_part, register_part
 from .spec import PartSpec
 
 
@@ -51,13 +51,27 @@ class ParallelMixers(Mixer):
         needs = [n for m in self.branches for n in _needs_of(m)]
         return tuple(needs) if needs else None
 
-    def forward(self, x, ctx, cache):
+    # Rows whose norm is half done go to every branch's first product; with a tail every branch's output product adds its
+    # share (scale_i x the tail's scale) into the residual itself, and the last one's view of the finished sum is the block's.
+    def accepts_normed(self, T):
+        return all(m.accepts_normed(T) for m in self.branches)
+
+    def fuses_tail(self, T):
+        return all(m.fuses_tail(T) for m in self.branches)
+
+    def forward(self, x, ctx, cache, tail=None):
         views = list(cache) if isinstance(cache, (tuple, list)) else ([] if cache is None else [cache])
         at, ys = 0, []
-        for m, n, single in zip(self.branches, self._n_needs, self._single):
+        for m, n, single, scale in zip(self.branches, self._n_needs, self._single, self.scales):
             mine = views[at: at + n]
             at += n
-            ys.append(m.forward(x, ctx, (mine[0] if mine else None) if single else tuple(mine)))
+            mine = (mine[0] if mine else None) if single else tuple(mine)
+            if tail is not None:
+                ys.append(m.forward(x, ctx, mine, tail=ResidualTail(tail.resid, tail.scale * scale, tail.norm)))
+            else:
+                ys.append(m.forward(x, ctx, mine))
+        if tail is not None:
+            return ys[-1]
         out = ctx.ws.rows("parallel_sum", x.shape[0], ys[0].shape[1], ys[0].dtype)
         ops.scaled_sum(ys[0], self.scales[0], ys[1], self.scales[1], out)
         for y, s in zip(ys[2:], self.scales[2:]):

@@ -119,6 +119,33 @@ def test_prompt_then_token_by_token(cuda_device, name, seed, dtype, graphs):
     eng.cache.check_invariants()
 
 
+@pytest.mark.parametrize("name,seed", CASES)
+def test_decode_steps_with_norms_in_the_products(cuda_device, name, seed, monkeypatch):
+    """A bfloat16 step of a few rows folds the norms into the products around them (the branches' output products add
+    into the residual, the first products divide by the rms): the mixers say they can, and the logits agree with the
+    step that runs the add + norm kernels."""
+    from infinilm_b200 import ops
+    from infinilm_b200.parts.blocks import PreNormResidual
+    raw = GOPITAR[name]()
+    w = make_weights(raw, seed)
+    ids = token_ids(60, raw["vocab"], 17)
+    outs = {}
+    for fused in (True, False):
+        monkeypatch.setattr(PreNormResidual, "FUSE_NORM", fused)
+        eng = _engine(raw, w, "bfloat16")
+        assert all(b.mixer.fuses_tail(4) and b.mixer.accepts_normed(4) and not b.mixer.fuses_tail(40) for b in eng.model.blocks)
+        calls = []
+        real = ops.gemm_skinny_resid
+        monkeypatch.setattr(ops, "gemm_skinny_resid", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+        outs[fused] = _run_cut(eng, ids, [40, 3] + [1] * 17)
+        monkeypatch.setattr(ops, "gemm_skinny_resid", real)
+        assert bool(calls) == fused
+        eng.synchronize()
+    ref = _oracle(name, seed, ids)
+    _check(outs[True], ref, "bfloat16", f"{name} fused")
+    _check(outs[False], ref, "bfloat16", f"{name} unfused")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,seed", CASES)
 def test_portions_of_changing_size(cuda_device, name, seed, dtype):
