@@ -254,82 +254,142 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld_q, int ld_k, int ld_v, int H, int G,
     int dim, int vdim, int in_act, const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
     float* state, size_t slot_stride, const int* __restrict__ read_slots, const int* __restrict__ write_slots,
-    const int* __restrict__ qstart, float* __restrict__ out, int ldo, int log_split, int e0) {
+    const int* __restrict__ qstart, float* __restrict__ out, int ldo, int log_split, int e0, int n_ent, int seg_len, float* seg_state) {
     extern __shared__ float sm[];
     constexpr int LOG_DPT = DPT == 8 ? 3 : DPT == 16 ? 4 : 5;
     constexpr int SEG = DPT + 4;                  // a lane's DPT values of q (or k) and 4 floats of padding: the lanes of a column then
                                                   // read their 16-byte pieces from different banks
-    const int split = 1 << log_split, dimp = DPT << log_split, log_dimp = log_split + LOG_DPT;
+    const int split = 1 << log_split, dimp = DPT << log_split;
     const int cpb = SR_THREADS >> log_split, log_cpb = 7 - log_split;
     const int row_f = SEG << log_split;           // floats of a staged token's q (or k)
     float* qs = sm;                               // [SR_CHUNK][split][SEG]
     float* ks = qs + SR_CHUNK * row_f;            // [SR_CHUNK][split][SEG]
     float* vs = ks + SR_CHUNK * row_f;            // [SR_CHUNK][cpb]
     float* gb = vs + SR_CHUNK * cpb;              // [2][SR_CHUNK]: g, beta
-    const int e = e0 + blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int h = blockIdx.y, tid = threadIdx.x;
     const int part = tid & (split - 1), col_l = tid >> log_split, c = blockIdx.z * cpb + col_l;
-    const int q0 = qstart[e], n = qstart[e + 1] - q0;
+    // Which tokens this block walks. Plain form (seg_len 0): entry e0 + blockIdx.x, all of it. Segmented form (the decayed
+    // sum of long portions): blockIdx.x counts segments of seg_len tokens, entry after entry; segment p of an entry starts
+    // from nothing (p > 0) and leaves what it gathered in seg_state, and a second pass (MODE 2) adds what the state at the
+    // segment's start contributes: S is linear in its start, o_t += decay^(t - t0 + 1) S_start^T q_t.
+    int e = e0 + blockIdx.x, q0, n, p = 0, n_seg = 1, first_tile = 0;
+    if (seg_len > 0) {
+        int tile = blockIdx.x;
+        for (e = e0;; ++e) {
+            if (e >= e0 + n_ent) return;          // a surplus block (the grid is a bound)
+            const int a = qstart[e], cnt = (qstart[e + 1] - a + seg_len - 1) / seg_len;
+            if (tile < cnt) {
+                p = tile, n_seg = cnt, first_tile = blockIdx.x - tile;
+                break;
+            }
+            tile -= cnt;
+        }
+        const int a = qstart[e], len = qstart[e + 1] - a;
+        q0 = a + p * seg_len;
+        n = min(seg_len, len - p * seg_len);
+        if (MODE == 2 && p == 0) return;          // the first segment started from the request's own state: nothing to add
+    } else {
+        q0 = qstart[e];
+        n = qstart[e + 1] - q0;
+    }
     if (n <= 0) return;
     const int hq = h / (H / G);
     const bool live = c < vdim;
     const int d0 = part * DPT;
     float S[DPT];
-    {
-        const float* rd = state + (size_t)read_slots[e] * slot_stride + ((size_t)h * vdim + c) * dim;
+    const float dec = MODE != 1 ? decay[h] : 0.f;
+    auto load_cols = [&](const float* src, float* dst) {      // this lane's DPT rows of column c from a [vdim][dim] matrix
         if (live && (dim & 3) == 0) {             // a column's rows lie together: 16 bytes a load (dim a multiple of 4 keeps them aligned)
 #pragma unroll
             for (int i = 0; i < DPT; i += 4) {
-                const float4 x = d0 + i < dim ? *reinterpret_cast<const float4*>(rd + d0 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-                S[i] = x.x, S[i + 1] = x.y, S[i + 2] = x.z, S[i + 3] = x.w;
+                const float4 x = d0 + i < dim ? *reinterpret_cast<const float4*>(src + (size_t)c * dim + d0 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                dst[i] = x.x, dst[i + 1] = x.y, dst[i + 2] = x.z, dst[i + 3] = x.w;
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) S[i] = (live && d0 + i < dim) ? rd[d0 + i] : 0.f;
+            for (int i = 0; i < DPT; ++i) dst[i] = (live && d0 + i < dim) ? src[(size_t)c * dim + d0 + i] : 0.f;
         }
+    };
+    auto store_cols = [&](float* dst, const float* src) {
+        if (!live) return;
+        if ((dim & 3) == 0) {
+#pragma unroll
+            for (int i = 0; i < DPT; i += 4)
+                if (d0 + i < dim) *reinterpret_cast<float4*>(dst + (size_t)c * dim + d0 + i) = make_float4(src[i], src[i + 1], src[i + 2], src[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < DPT; ++i)
+                if (d0 + i < dim) dst[(size_t)c * dim + d0 + i] = src[i];
+        }
+    };
+    const size_t head_f = (size_t)dim * vdim;     // floats of one head's state
+    if (MODE == 2) {
+        // the state at this segment's start: what the segments before it gathered, each decayed over those behind it
+        const float dseg = powf(dec, (float)seg_len);
+        load_cols(seg_state + ((size_t)first_tile * H + h) * head_f, S);
+        for (int j = 1; j < p; ++j) {
+            float L[DPT];
+            load_cols(seg_state + ((size_t)(first_tile + j) * H + h) * head_f, L);
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) S[i] = fmaf(dseg, S[i], L[i]);
+        }
+        if (p == n_seg - 1) {                     // the last segment also leaves the request's state: its start decayed over it, plus its own
+            float L[DPT];
+            load_cols(seg_state + ((size_t)(first_tile + p) * H + h) * head_f, L);
+            const float dn = powf(dec, (float)n);
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) L[i] = fmaf(dn, S[i], L[i]);
+            store_cols(state + (size_t)write_slots[e] * slot_stride + (size_t)h * head_f, L);
+        }
+    } else if (p == 0) {
+        load_cols(state + (size_t)read_slots[e] * slot_stride + (size_t)h * head_f, S);
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) S[i] = 0.f;
     }
-    const float dec = MODE == 0 ? decay[h] : 0.f;
-    constexpr int NQ = (SR_CHUNK * DPT * SR_MAX_SPLIT + SR_THREADS - 1) / SR_THREADS;    // staged q (and k) values per thread at the widest split
-    constexpr int NV = SR_CHUNK;                           // staged v values per thread at split 1
+    // Staging: a token's values are fetched by TPT = 128 / SR_CHUNK neighbouring threads, thread l of them taking entries
+    // l, l + TPT, ...: one base address a chunk, then constant strides, in global and in shared memory alike.
+    constexpr int TPT = SR_THREADS / SR_CHUNK;
+    constexpr int NQ = (DPT * SR_MAX_SPLIT + TPT - 1) / TPT;       // q (and k) values per thread at the widest split
+    constexpr int NV = (SR_THREADS + TPT - 1) / TPT;               // v values per thread at split 1
+    static_assert(TPT >= DPT, "a staging thread's entries must fall into whole lane segments");
     float qr[NQ], kr[NQ], vr[NV], gr = 0.f;
-    const int n_qk = SR_CHUNK << log_dimp, n_v = SR_CHUNK << log_cpb;
+    const int s_tt = tid / TPT, s_l = tid % TPT;
+    const int s_at = s_tt * row_f + (s_l >> LOG_DPT) * SEG + (s_l & (DPT - 1));   // + j * (TPT >> LOG_DPT) * SEG
 
     auto fetch = [&](int t0) {                    // the chunk's values into registers (zeros beyond the entry's end and in padding)
-        const int nt = min(SR_CHUNK, n - t0);
+        const bool tok = t0 + s_tt < n;
+        const size_t row = (size_t)(q0 + t0 + s_tt);
+        const float* qp = q + row * ld_q + hq * dim + s_l;
+        const float* kp = k + row * ld_k + hq * dim + s_l;
 #pragma unroll
         for (int j = 0; j < NQ; ++j) {
-            const int idx = tid + j * SR_THREADS;
-            const int tt = idx >> log_dimp, d = idx & (dimp - 1);
-            const bool ok = idx < n_qk && tt < nt && d < dim;
-            const size_t row = (size_t)(q0 + t0 + tt);
-            qr[j] = ok ? q[row * ld_q + hq * dim + d] : 0.f;
-            kr[j] = ok ? k[row * ld_k + hq * dim + d] : 0.f;
+            const bool ok = tok && s_l + j * TPT < dim;
+            qr[j] = ok ? qp[j * TPT] : 0.f;
+            kr[j] = (MODE != 2 && ok) ? kp[j * TPT] : 0.f;
         }
+        if (MODE != 2) {
+            const float* vp = v + row * ld_v + h * vdim + blockIdx.z * cpb + s_l;
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int idx = tid + j * SR_THREADS;
-            const int tt = idx >> log_cpb, cc = blockIdx.z * cpb + (idx & (cpb - 1));
-            vr[j] = (idx < n_v && tt < nt && cc < vdim) ? v[(size_t)(q0 + t0 + tt) * ld_v + h * vdim + cc] : 0.f;
+            for (int j = 0; j < NV; ++j)
+                vr[j] = (tok && s_l + j * TPT < cpb && blockIdx.z * cpb + s_l + j * TPT < vdim) ? vp[j * TPT] : 0.f;
         }
         if (MODE == 1 && tid < 2 * SR_CHUNK) {
             const int tt = tid & (SR_CHUNK - 1);
-            gr = tt < nt ? (tid < SR_CHUNK ? gdec : beta)[(size_t)(q0 + t0 + tt) * H + h] : 0.f;
+            gr = t0 + tt < n ? (tid < SR_CHUNK ? gdec : beta)[(size_t)(q0 + t0 + tt) * H + h] : 0.f;
         }
     };
     auto stage = [&]() {                          // registers to shared memory, the activation applied once per value
 #pragma unroll
-        for (int j = 0; j < NQ; ++j) {
-            const int idx = tid + j * SR_THREADS;
-            if (idx < n_qk) {
-                const int tt = idx >> log_dimp, d = idx & (dimp - 1);
-                const int at = tt * row_f + (d >> LOG_DPT) * SEG + (d & (DPT - 1));
-                qs[at] = in_act ? sm_silu_fast(qr[j]) : qr[j];
-                ks[at] = in_act ? sm_silu_fast(kr[j]) : kr[j];
+        for (int j = 0; j < NQ; ++j)
+            if (s_l + j * TPT < dimp) {
+                qs[s_at + j * (TPT >> LOG_DPT) * SEG] = in_act ? sm_silu_fast(qr[j]) : qr[j];
+                if (MODE != 2) ks[s_at + j * (TPT >> LOG_DPT) * SEG] = in_act ? sm_silu_fast(kr[j]) : kr[j];
             }
-        }
+        if (MODE != 2) {
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int idx = tid + j * SR_THREADS;
-            if (idx < n_v) vs[idx] = in_act ? sm_silu_fast(vr[j]) : vr[j];
+            for (int j = 0; j < NV; ++j)
+                if (s_l + j * TPT < cpb) vs[(s_tt << log_cpb) + s_l + j * TPT] = in_act ? sm_silu_fast(vr[j]) : vr[j];
         }
         if (MODE == 1 && tid < 2 * SR_CHUNK) gb[tid] = gr;
     };
@@ -343,16 +403,27 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     for (int t0 = 0; t0 < n; t0 += SR_CHUNK) {
         const int nt = min(SR_CHUNK, n - t0);
         if (t0 + SR_CHUNK < n) fetch(t0 + SR_CHUNK);
-        float oacc[SR_CHUNK];
+        float oacc[SR_CHUNK], oold[MODE == 2 ? SR_CHUNK : 1];
+        if (MODE == 2 && live && part == 0) {     // what the first pass wrote, asked for before the products
+#pragma unroll
+            for (int tt = 0; tt < SR_CHUNK; ++tt) oold[tt] = tt < nt ? out[(size_t)(q0 + t0 + tt) * ldo + h * vdim + c] : 0.f;
+        }
 #pragma unroll
         for (int tt = 0; tt < SR_CHUNK; ++tt) {
             oacc[tt] = 0.f;
             if (tt < nt) {
                 const float4* qq = reinterpret_cast<const float4*>(qs + tt * row_f + part * SEG);
                 const float4* kk = reinterpret_cast<const float4*>(ks + tt * row_f + part * SEG);
-                const float vc = vs[(tt << log_cpb) + col_l];
+                const float vc = MODE != 2 ? vs[(tt << log_cpb) + col_l] : 0.f;
                 float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-                if (MODE == 0) {
+                if (MODE == 2) {
+#pragma unroll
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        const float4 q4 = qq[i];
+                        o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                        o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                    }
+                } else if (MODE == 0) {
 #pragma unroll
                     for (int i = 0; i < DPT / 4; ++i) {
                         const float4 k4 = kk[i], q4 = qq[i];
@@ -400,25 +471,27 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
                 for (int tt = 0; tt < SR_CHUNK; ++tt) oacc[tt] += __shfl_xor_sync(0xffffffffu, oacc[tt], m);
             }
         if (live && part == 0) {
+            if (MODE == 2) {                      // token i of the segment sees its start through i + 1 decays
+                float pw = powf(dec, (float)(t0 + 1));
 #pragma unroll
-            for (int tt = 0; tt < SR_CHUNK; ++tt)
-                if (tt < nt) out[(size_t)(q0 + t0 + tt) * ldo + h * vdim + c] = oacc[tt];
+                for (int tt = 0; tt < SR_CHUNK; ++tt) {
+                    if (tt < nt) out[(size_t)(q0 + t0 + tt) * ldo + h * vdim + c] = fmaf(pw, oacc[tt], oold[tt]);
+                    pw *= dec;
+                }
+            } else {
+#pragma unroll
+                for (int tt = 0; tt < SR_CHUNK; ++tt)
+                    if (tt < nt) out[(size_t)(q0 + t0 + tt) * ldo + h * vdim + c] = oacc[tt];
+            }
         }
         __syncthreads();                          // everyone has read this chunk
         if (t0 + SR_CHUNK < n) stage();
         __syncthreads();
     }
-    if (live) {
-        float* wr = state + (size_t)write_slots[e] * slot_stride + ((size_t)h * vdim + c) * dim;
-        if ((dim & 3) == 0) {
-#pragma unroll
-            for (int i = 0; i < DPT; i += 4)
-                if (d0 + i < dim) *reinterpret_cast<float4*>(wr + d0 + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < DPT; ++i)
-                if (d0 + i < dim) wr[d0 + i] = S[i];
-        }
+    if (MODE != 2) {
+        // what this block gathered: the request's state, or - a segment of several - its share for the second pass
+        if (n_seg == 1) store_cols(state + (size_t)write_slots[e] * slot_stride + (size_t)h * head_f, S);
+        else store_cols(seg_state + ((size_t)blockIdx.x * H + h) * head_f, S);
     }
 }
 
@@ -426,10 +499,10 @@ template <int MODE, int DPT, int CH, int MS>
 static void sr_launch(dim3 grid, size_t smem, cudaStream_t stream, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v,
                       int H, int G, int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
                       size_t slot_stride, const int* read_slots, const int* write_slots, const int* qstart, float* out, int ldo, int log_split,
-                      int e0) {
+                      int e0, int n_ent, int seg_len, float* seg_state) {
     matrix_state_scan_reg_kernel<MODE, DPT, CH, MS><<<grid, SR_THREADS, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta,
                                                                                     gdec, state, slot_stride, read_slots, write_slots, qstart, out,
-                                                                                    ldo, log_split, e0);
+                                                                                    ldo, log_split, e0, n_ent, seg_len, seg_state);
 }
 
 // In place: x[t, c] = silu(x[t, c]) for the first `cols` columns of float32 rows (the recurrences' inputs, as a pass of its own).
@@ -452,9 +525,13 @@ IL_EXPORT int il_silu_cols(float* x, int ld, int cols, int T, cudaStream_t strea
 IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v, int H, int G,
                                    int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
                                    long long slot_stride, const int* read_slots, const int* write_slots, const int* qstart, int E,
-                                   float* out, int ldo, int generic, int e0, int single, cudaStream_t stream) {
+                                   float* out, int ldo, int generic, int e0, int single, int seg_len, int n_tiles, float* seg_state,
+                                   cudaStream_t stream) {
     if (E <= 0) return IL_OK;
     if (e0 < 0) return IL_BAD_ARG;
+    // seg_len > 0 (decayed sum, register form only): the entries' tokens in segments of seg_len, n_tiles of them at most
+    // (a bound is enough), seg_state float32 [n_tiles, H, vdim, dim] scratch; two passes.
+    if (seg_len > 0 && (mode != 0 || generic || single || dim > 256 || n_tiles <= 0 || !seg_state || seg_len % 8)) return IL_BAD_ARG;
     if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1)) return IL_BAD_ARG;
     if (mode == 0 ? !decay : (!beta || !gdec)) return IL_BAD_ARG;
     if (dim <= 256 && !generic) {
@@ -465,16 +542,16 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
         int dpt = dim <= 32 ? 8 : 16;
         if (mode == 0 && dim > 32 && dim <= 128) {
             const int cols16 = SR_THREADS / ((dim + 15) / 16 <= 1 ? 1 : (dim <= 32 ? 2 : dim <= 64 ? 4 : 8));
-            if ((long long)E * H * ((vdim + cols16 - 1) / cols16) <= 148) dpt = 8;     // at most one block an SM otherwise
+            if ((long long)(seg_len > 0 ? n_tiles : E) * H * ((vdim + cols16 - 1) / cols16) <= 148) dpt = 8;     // at most one block an SM otherwise
         }
         int log_split = 0;
         while ((dpt << log_split) < dim) ++log_split;
         const int cpb = SR_THREADS >> log_split;
         const int ch = single ? 1 : 8;
         const size_t smem_r = ((size_t)ch * (2 * ((dpt + 4) << log_split) + cpb) + 2 * ch) * sizeof(float);
-        const dim3 grid_r(E, H, (vdim + cpb - 1) / cpb);
+        const dim3 grid_r(seg_len > 0 ? n_tiles : E, H, (vdim + cpb - 1) / cpb);
 #define SR_ARGS grid_r, smem_r, stream, q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state, (size_t)slot_stride, \
-                read_slots, write_slots, qstart, out, ldo, log_split, e0
+                read_slots, write_slots, qstart, out, ldo, log_split, e0, E, seg_len, seg_state
         // (the widest split a variant is built for sizes its staging registers: 8 lanes up to dim = 8 DPT, 16 beyond)
 #define SR_PICK(MODE_, DPT_)                                                                                     \
         do {                                                                                                     \
@@ -483,6 +560,11 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
         } while (0)
         if (mode == 0) {
             if (dpt == 8) SR_PICK(0, 8); else SR_PICK(0, 16);
+            if (seg_len > 0) {                    // the second pass: what each segment's start contributes
+                IL_LAUNCH_CHECK();
+                if (log_split <= 3) { if (dpt == 8) sr_launch<2, 8, 8, 8>(SR_ARGS); else sr_launch<2, 16, 8, 8>(SR_ARGS); }
+                else { if (dpt == 8) sr_launch<2, 8, 8, 16>(SR_ARGS); else sr_launch<2, 16, 8, 16>(SR_ARGS); }
+            }
         } else {
             if (dpt == 8) SR_PICK(1, 8); else SR_PICK(1, 16);
         }

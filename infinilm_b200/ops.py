@@ -1038,14 +1038,17 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
                       vdim: int, in_act: int, decay: Optional[torch.Tensor], beta: Optional[torch.Tensor],
                       gdec: Optional[torch.Tensor], state: torch.Tensor, read_slots: torch.Tensor, write_slots: torch.Tensor,
                       entry_qstart: torch.Tensor, n_entries: int, out: torch.Tensor, generic: bool = False, first_entry: int = 0,
-                      single: bool = False) -> None:
+                      single: bool = False, seg_len: int = 0, n_tiles: int = 0, seg_state: Optional[torch.Tensor] = None) -> None:
     """A recurrence over a float32 state S [dim, vdim] per (request, head), token by token in each entry's order.
     SCAN_DECAY: S = decay[h] S + k v^T, o = S^T q. SCAN_DELTA: S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q.
     q, k float32 [T, >= n_qk_heads*dim] (views with a row stride), v float32 [T, >= n_heads*vdim], out float32 [T, n_heads*vdim];
     value head h reads q/k head h // (n_heads // n_qk_heads). in_act 1: silu on q, k, v as read.
     state float32 [slots, n_heads, vdim, dim] (S column by column: the dim entries behind one output lie together). `generic`: the kernel that keeps the state in shared memory (any size; the
     one that runs beyond a key size of 256) instead of the one that keeps it in registers. Entries first_entry ..
-    first_entry + n_entries - 1 are run; `single`: each of them brings one token (the form made for decoding)."""
+    first_entry + n_entries - 1 are run; `single`: each of them brings one token (the form made for decoding).
+    seg_len > 0 (SCAN_DECAY, key sizes up to 256): every entry's tokens are walked in segments of seg_len at once, each from
+    nothing, and a second launch adds what the state at a segment's start contributes (the sum is linear in it);
+    `n_tiles` bounds the number of segments, `seg_state` is float32 scratch of n_tiles * heads * vdim * dim."""
     _need_cuda(q, k, v, decay, beta, gdec, state, read_slots, write_slots, entry_qstart, out)
     _i32("matrix_state_scan", read_slots, write_slots, entry_qstart)
     for t in (q, k, v, out, state):
@@ -1055,22 +1058,42 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
         raise KernelError("matrix_state_scan: state float32 [slots, heads, vdim, dim]")
     if out.shape[1] != n_heads * vdim or q.shape[1] < n_qk_heads * dim or k.shape[1] < n_qk_heads * dim or v.shape[1] < n_heads * vdim:
         raise KernelError("matrix_state_scan: shapes")
+    if seg_len > 0:
+        _need_cuda(seg_state)
+        if (mode != SCAN_DECAY or generic or single or dim > 256 or seg_len % 8 or n_tiles <= 0 or seg_state is None
+                or seg_state.dtype != torch.float32 or not seg_state.is_contiguous() or seg_state.numel() < n_tiles * n_heads * vdim * dim):
+            raise KernelError("matrix_state_scan: segments go with SCAN_DECAY in the register form and float32 scratch for n_tiles states")
     f = _fn("seqmix", "il_matrix_state_scan", [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p,
-                                               _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+                                               _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                               _c_void_p])
     _check(f(mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), n_heads, n_qk_heads, dim, vdim, in_act,
              _ptr(decay), _ptr(beta), _ptr(gdec), _ptr(state), state.stride(0), _ptr(read_slots), _ptr(write_slots),
-             _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), int(generic), first_entry, int(single), _stream()), "matrix_state_scan")
+             _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), int(generic), first_entry, int(single), seg_len, n_tiles,
+             _ptr(seg_state), _stream()), "matrix_state_scan")
+    if seg_len > 0:
+        count_launches(1)                         # the second pass
 
 
 def matrix_state_scan_step(ctx, *args, **kw) -> None:
     """`matrix_state_scan` over a step's entries: the single tokens (the first `ctx.n_decode` entries) by the form made for
-    them, the prompt portions behind them by the chunked form."""
+    them, the prompt portions behind them by the chunked form - the decayed sum of long portions in segments that run at
+    once (`SCAN_SEGMENT` tokens; the choice rests on the step's shape alone, so a replayed step makes it the same way)."""
     n_dec, E = ctx.n_decode, ctx.n_entries
     if n_dec > 0:
         matrix_state_scan(*args, n_entries=n_dec, first_entry=0, single=True, **kw)
     if E > n_dec:
-        matrix_state_scan(*args, n_entries=E - n_dec, first_entry=n_dec, single=False, **kw)
+        mode, dim, vdim, n_heads = args[0], args[6], args[7], args[4]
+        if (mode == SCAN_DECAY and not kw.get("generic") and dim <= 256 and ctx.T - n_dec >= 2 * SCAN_SEGMENT):
+            n_tiles = ctx.prompt_tiles(SCAN_SEGMENT)
+            scratch = ctx.ws.flat("scan_segment_state", n_tiles * n_heads * vdim * dim, torch.float32)
+            matrix_state_scan(*args, n_entries=E - n_dec, first_entry=n_dec, single=False, seg_len=SCAN_SEGMENT, n_tiles=n_tiles,
+                              seg_state=scratch, **kw)
+        else:
+            matrix_state_scan(*args, n_entries=E - n_dec, first_entry=n_dec, single=False, **kw)
+
+
+SCAN_SEGMENT = 128
 
 
 def silu_cols(x: torch.Tensor, cols: int) -> None:

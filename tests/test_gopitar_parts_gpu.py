@@ -178,7 +178,7 @@ def test_scan_of_a_batch_equals_each_alone(cuda_device, scan_kernel):
     st2, out2 = before.clone(), torch.empty(T2, H * dv, device=dev)
 
     class Ctx:
-        n_decode, n_entries = 2, 4
+        n_decode, n_entries, T = 2, 4, T2
     ops.matrix_state_scan_step(Ctx, ops.SCAN_DECAY, q[:T2], k[:T2], v[:T2], H, H, d, dv, 0, decay, None, None, st2, rd, wr, qs2, out=out2, generic=GENERIC)
     a = 0
     for e, n in enumerate(lens2):
@@ -186,6 +186,42 @@ def test_scan_of_a_batch_equals_each_alone(cuda_device, scan_kernel):
         one = _scan(ops, ops.SCAN_DECAY, q[a:a + n], k[a:a + n], v[a:a + n], H, H, d, dv, decay, None, None, st, int(wr[e]), int(rd[e]) == 0, dev)
         assert torch.equal(one, out2[a:a + n]) and torch.equal(st[int(wr[e])], st2[int(wr[e])])
         a += n
+
+
+@pytest.mark.parametrize("H,d,dv", [(2, 32, 32), (3, 8, 40), (1, 128, 64), (2, 20, 12)])
+def test_decayed_sum_in_segments(cuda_device, H, d, dv):
+    """Long portions walked in segments that run at once, with the second pass that adds each segment's start: several
+    entries of unequal length (one segment, an exact multiple, a ragged end), from states that hold something, against
+    the plain implementation continued from those states; the request's state afterwards too."""
+    from infinilm_b200 import ops
+    dev = cuda_device
+    torch.manual_seed(H + d)
+    seg, lens = 64, [200, 64, 7, 129, 128]
+    T = sum(lens)
+    q, k, v = torch.randn(T, H * d) * 0.5, torch.randn(T, H * d) * 0.5, torch.randn(T, H * dv)
+    decay = torch.tensor([0.999, 0.7, 0.97][:H])
+    state = torch.randn(8, H, dv, d, device=dev) * 0.3
+    state[0] = 0
+    rd, wr = _i32([1, 0, 2, 0, 3], dev), _i32([1, 4, 2, 5, 3], dev)
+    before = state.clone()
+    qstart, _ = _step_arrays(lens, dev)
+    out = torch.empty(T, H * dv, device=dev)
+    n_tiles = sum((n + seg - 1) // seg for n in lens) + 2        # a bound: surplus blocks leave
+    scratch = torch.empty(n_tiles * H * dv * d, device=dev)
+    ops.matrix_state_scan(ops.SCAN_DECAY, q.to(dev), k.to(dev), v.to(dev), H, H, d, dv, 0, decay.to(dev), None, None, state, rd, wr, qstart,
+                          len(lens), out, seg_len=seg, n_tiles=n_tiles, seg_state=scratch)
+    a = 0
+    for e, n in enumerate(lens):
+        S = before[int(rd[e])].cpu().double().transpose(1, 2).clone()          # [H, d, dv]
+        want = torch.zeros(n, H, dv, dtype=torch.float64)
+        for t in range(n):
+            S = decay.double()[:, None, None] * S + k[a + t].double().view(H, d)[:, :, None] * v[a + t].double().view(H, dv)[:, None, :]
+            want[t] = torch.einsum("hde,hd->he", S, q[a + t].double().view(H, d))
+        got = out[a:a + n].cpu().double().view(n, H, dv)
+        assert float((got - want).abs().max()) <= 3e-5 * float(want.abs().max()), (e, n)
+        assert float((state[int(wr[e])].cpu().double().transpose(1, 2) - S).abs().max()) <= 3e-5 * float(S.abs().max()), (e, n)
+        a += n
+    assert torch.equal(state[6], before[6]) and torch.equal(state[7], before[7])
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
