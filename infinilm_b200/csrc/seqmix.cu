@@ -25,31 +25,40 @@ __device__ __forceinline__ float sm_silu_fast(float z) { return __fdividef(z, 1.
 // (heads padded to a common size). One thread per (row, output column).
 template <typename TI, typename TO>
 __global__ void short_conv_kernel(const TI* __restrict__ x, int ldx, int x_off, const float* __restrict__ w, int taps,
-                                  const float* __restrict__ state, size_t slot_stride, int st_off, int st_ld,
-                                  const int* __restrict__ read_slots, const int* __restrict__ tok_entry,
+                                  float* state, size_t slot_stride, int st_off, int st_ld,
+                                  const int* __restrict__ read_slots, const int* __restrict__ write_slots, const int* __restrict__ tok_entry,
                                   const int* __restrict__ qstart, TO* __restrict__ out, int ldo, int out_off, int n_seg, int seg_in,
-                                  int seg_out, int act, int T) {
-    const int cols = n_seg * seg_out;
+                                  int n_seg2, int seg_in2, int seg_out, int act, int T) {
+    // columns: n_seg segments of seg_in channels, then n_seg2 of seg_in2, every segment written seg_out wide
+    const int cols = (n_seg + n_seg2) * seg_out;
     const size_t total = (size_t)T * cols;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / cols), oc = (int)(idx - (size_t)t * cols);
         const int seg = oc / seg_out, within = oc - seg * seg_out;
+        const bool second = seg >= n_seg;
+        const int width = second ? seg_in2 : seg_in;
         TO* o = out + (size_t)t * ldo + out_off + oc;
-        if (within >= seg_in) {
+        if (within >= width) {
             *o = il_from_f<TO>(0.f);
             continue;
         }
-        const int ch = seg * seg_in + within;
+        const int ch = second ? n_seg * seg_in + (seg - n_seg) * seg_in2 + within : seg * seg_in + within;
         const int e = tok_entry[t];
-        const int local = t - qstart[e];
-        const float* st = state + (size_t)read_slots[e] * slot_stride + st_off + ch;
-        float acc = 0.f;
+        const int first = qstart[e], local = t - first;
+        const bool alone = write_slots && qstart[e + 1] - first == 1;     // the entry's only token: this thread also moves the state on
+        float* st = state + (size_t)read_slots[e] * slot_stride + st_off + ch;
+        float acc = 0.f, keep[SM_MAX_TAPS];
         for (int j = 0; j < taps; ++j) {
             const int s = local - (taps - 1) + j;
             const float u = s >= 0 ? il_to_f(x[(size_t)(t - local + s) * ldx + x_off + ch]) : st[(size_t)(taps - 1 + s) * st_ld];
             acc = fmaf(w[(size_t)ch * taps + j], u, acc);
+            keep[j] = u;
         }
         *o = il_from_f<TO>(act == 1 ? sm_silu(acc) : acc);
+        if (alone) {                              // nobody else reads this entry's state for this channel: safe in place
+            float* wr = state + (size_t)write_slots[e] * slot_stride + st_off + ch;
+            for (int j = 1; j < taps; ++j) wr[(size_t)(j - 1) * st_ld] = keep[j];
+        }
     }
 }
 
@@ -58,10 +67,10 @@ __global__ void short_conv_kernel(const TI* __restrict__ x, int ldx, int x_off, 
 template <typename TI>
 __global__ void short_conv_state_kernel(const TI* __restrict__ x, int ldx, int x_off, int C, int taps, float* state,
                                         size_t slot_stride, int st_off, int st_ld, const int* __restrict__ read_slots,
-                                        const int* __restrict__ write_slots, const int* __restrict__ qstart, int E) {
+                                        const int* __restrict__ write_slots, const int* __restrict__ qstart, int E, int e0) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= E * C) return;
-    const int e = idx / C, ch = idx - e * C;
+    const int e = e0 + idx / C, ch = idx % C;
     const int q0 = qstart[e], n = qstart[e + 1] - q0;
     if (n <= 0) return;
     const float* rd = state + (size_t)read_slots[e] * slot_stride + st_off + ch;
@@ -79,15 +88,18 @@ static inline int sm_grid(size_t total, int threads) {
     return (int)(g > 148 * 32 ? 148 * 32 : (g < 1 ? 1 : g));
 }
 
-IL_EXPORT int il_short_conv(const void* x, int x_kind, int ldx, int x_off, const float* w, int taps, const float* state,
-                            long long slot_stride, int st_off, int st_ld, const int* read_slots, const int* tok_entry,
-                            const int* qstart, void* out, int out_kind, int ldo, int out_off, int n_seg, int seg_in, int seg_out,
-                            int act, int T, cudaStream_t stream) {
+// write_slots (may be null): entries that bring a single token get their state moved on by this kernel; the others (and
+// all of them, without write_slots) by il_short_conv_state.
+IL_EXPORT int il_short_conv(const void* x, int x_kind, int ldx, int x_off, const float* w, int taps, float* state,
+                            long long slot_stride, int st_off, int st_ld, const int* read_slots, const int* write_slots, const int* tok_entry,
+                            const int* qstart, void* out, int out_kind, int ldo, int out_off, int n_seg, int seg_in, int n_seg2, int seg_in2,
+                            int seg_out, int act, int T, cudaStream_t stream) {
     if (T <= 0 || n_seg <= 0) return IL_OK;
-    if (taps < 1 || taps > SM_MAX_TAPS || seg_in <= 0 || seg_out < seg_in) return IL_BAD_ARG;
-    const int grid = sm_grid((size_t)T * n_seg * seg_out, 256);
-#define SC_ARGS ldx, x_off, w, taps, state, (size_t)slot_stride, st_off, st_ld, read_slots, tok_entry, qstart
-#define SC_TAIL ldo, out_off, n_seg, seg_in, seg_out, act, T
+    if (taps < 1 || taps > SM_MAX_TAPS || seg_in <= 0 || seg_out < seg_in || n_seg2 < 0 || (n_seg2 > 0 && (seg_in2 <= 0 || seg_out < seg_in2)))
+        return IL_BAD_ARG;
+    const int grid = sm_grid((size_t)T * (n_seg + n_seg2) * seg_out, 256);
+#define SC_ARGS ldx, x_off, w, taps, state, (size_t)slot_stride, st_off, st_ld, read_slots, write_slots, tok_entry, qstart
+#define SC_TAIL ldo, out_off, n_seg, seg_in, n_seg2, seg_in2, seg_out, act, T
     if (x_kind == IL_F32 && out_kind == IL_F32)
         short_conv_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)x, SC_ARGS, (float*)out, SC_TAIL);
     else if (x_kind == IL_BF16 && out_kind == IL_F32)
@@ -100,18 +112,19 @@ IL_EXPORT int il_short_conv(const void* x, int x_kind, int ldx, int x_off, const
     return IL_OK;
 }
 
+// Entries e0 .. e0 + E - 1.
 IL_EXPORT int il_short_conv_state(const void* x, int x_kind, int ldx, int x_off, int C, int taps, float* state, long long slot_stride,
-                                  int st_off, int st_ld, const int* read_slots, const int* write_slots, const int* qstart, int E,
+                                  int st_off, int st_ld, const int* read_slots, const int* write_slots, const int* qstart, int E, int e0,
                                   cudaStream_t stream) {
     if (E <= 0 || C <= 0 || taps <= 1) return IL_OK;
-    if (taps > SM_MAX_TAPS) return IL_BAD_ARG;
+    if (taps > SM_MAX_TAPS || e0 < 0) return IL_BAD_ARG;
     const int grid = (E * C + 255) / 256;
     if (x_kind == IL_F32)
         short_conv_state_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, ldx, x_off, C, taps, state, (size_t)slot_stride, st_off, st_ld,
-                                                                 read_slots, write_slots, qstart, E);
+                                                                 read_slots, write_slots, qstart, E, e0);
     else if (x_kind == IL_BF16)
         short_conv_state_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, x_off, C, taps, state, (size_t)slot_stride,
-                                                                         st_off, st_ld, read_slots, write_slots, qstart, E);
+                                                                         st_off, st_ld, read_slots, write_slots, qstart, E, e0);
     else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

@@ -972,33 +972,40 @@ def _i32(name: str, *ts: torch.Tensor) -> None:
 
 def short_conv(x: torch.Tensor, x_off: int, w: torch.Tensor, state: torch.Tensor, st_off: int, read_slots: torch.Tensor,
                tok_entry: torch.Tensor, entry_qstart: torch.Tensor, out: torch.Tensor, out_off: int, n_seg: int, seg_in: int,
-               seg_out: int, act: int = 0) -> None:
-    """Causal convolution over time of n_seg * seg_in channels of `x` (columns from x_off), per channel, with weights
-    w float32 [channels, taps] whose last column meets the current token. Inputs before a step's first row come from
-    `state` (float32 [slots, taps-1, all channels], this call's channels from column st_off; slot read_slots[entry]).
-    Written to `out` from column out_off as n_seg segments of seg_out >= seg_in columns, the surplus zero. act 1: silu."""
-    _need_cuda(x, w, state, read_slots, tok_entry, entry_qstart, out)
+               seg_out: int, act: int = 0, n_seg2: int = 0, seg_in2: int = 0, write_slots: Optional[torch.Tensor] = None) -> None:
+    """Causal convolution over time of n_seg * seg_in (+ n_seg2 * seg_in2) channels of `x` (columns from x_off), per channel,
+    with weights w float32 [channels, taps] whose last column meets the current token. Inputs before a step's first row come
+    from `state` (float32 [slots, taps-1, all channels], this call's channels from column st_off; slot read_slots[entry]).
+    Written to `out` from column out_off as segments of seg_out columns each, the surplus zero. act 1: silu.
+    `write_slots`: entries that bring ONE token have their state moved on here, in slot write_slots[entry] (the thread that
+    reads such an entry's state is the only one that does); `short_conv_state` then only has the other entries to do."""
+    _need_cuda(x, w, state, read_slots, tok_entry, entry_qstart, out, write_slots)
     _i32("short_conv", read_slots, tok_entry, entry_qstart)
+    if write_slots is not None:
+        _i32("short_conv", write_slots)
     T, taps = x.shape[0], w.shape[1]
-    if w.dtype != torch.float32 or not w.is_contiguous() or w.shape[0] != n_seg * seg_in:
+    n_ch = n_seg * seg_in + n_seg2 * seg_in2
+    if w.dtype != torch.float32 or not w.is_contiguous() or w.shape[0] != n_ch:
         raise KernelError("short_conv: w float32 [channels, taps]")
     if state.dtype != torch.float32 or not state.is_contiguous() or state.dim() != 3 or state.shape[1] != max(taps - 1, 1):
         raise KernelError("short_conv: state float32 [slots, taps-1, channels]")
-    if (x.stride(1) != 1 or out.stride(1) != 1 or out.shape[0] != T or x_off + n_seg * seg_in > x.shape[1]
-            or out_off + n_seg * seg_out > out.shape[1] or st_off + n_seg * seg_in > state.shape[2]):
+    if (x.stride(1) != 1 or out.stride(1) != 1 or out.shape[0] != T or x_off + n_ch > x.shape[1]
+            or out_off + (n_seg + n_seg2) * seg_out > out.shape[1] or st_off + n_ch > state.shape[2]):
         raise KernelError("short_conv: column ranges do not fit")
     f = _fn("seqmix", "il_short_conv", [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_ll, _c_int, _c_int,
-                                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                        _c_int, _c_int, _c_void_p])
+                                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), x_off, _ptr(w), taps, _ptr(state), state.stride(0), st_off, state.shape[2],
-             _ptr(read_slots), _ptr(tok_entry), _ptr(entry_qstart), _ptr(out), kind_of(out.dtype), out.stride(0), out_off, n_seg,
-             seg_in, seg_out, act, T, _stream()), "short_conv")
+             _ptr(read_slots), _ptr(write_slots if taps > 1 else None), _ptr(tok_entry), _ptr(entry_qstart), _ptr(out), kind_of(out.dtype),
+             out.stride(0), out_off, n_seg, seg_in, n_seg2, seg_in2, seg_out, act, T, _stream()), "short_conv")
 
 
 def short_conv_state(x: torch.Tensor, x_off: int, n_channels: int, taps: int, state: torch.Tensor, st_off: int,
-                     read_slots: torch.Tensor, write_slots: torch.Tensor, entry_qstart: torch.Tensor, n_entries: int) -> None:
-    """The convolution's state after the step: the last taps-1 inputs of every entry, into slot write_slots[entry]."""
-    if taps <= 1:
+                     read_slots: torch.Tensor, write_slots: torch.Tensor, entry_qstart: torch.Tensor, n_entries: int,
+                     first_entry: int = 0) -> None:
+    """The convolution's state after the step: the last taps-1 inputs of entries first_entry .. first_entry + n_entries - 1,
+    into slot write_slots[entry]."""
+    if taps <= 1 or n_entries <= 0:
         return
     _need_cuda(x, state, read_slots, write_slots, entry_qstart)
     _i32("short_conv_state", read_slots, write_slots, entry_qstart)
@@ -1007,9 +1014,9 @@ def short_conv_state(x: torch.Tensor, x_off: int, n_channels: int, taps: int, st
     if x.stride(1) != 1 or x_off + n_channels > x.shape[1] or st_off + n_channels > state.shape[2]:
         raise KernelError("short_conv_state: column ranges do not fit")
     f = _fn("seqmix", "il_short_conv_state", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_ll, _c_int, _c_int,
-                                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p])
+                                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), x_off, n_channels, taps, _ptr(state), state.stride(0), st_off, state.shape[2],
-             _ptr(read_slots), _ptr(write_slots), _ptr(entry_qstart), n_entries, _stream()), "short_conv_state")
+             _ptr(read_slots), _ptr(write_slots), _ptr(entry_qstart), n_entries, first_entry, _stream()), "short_conv_state")
 
 
 def delta_prep(qk: torch.Tensor, q_off: int, k_off: int, n_qk_heads: int, dim: int, q_scale: float, unit_eps: float,

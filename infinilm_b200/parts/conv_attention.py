@@ -110,8 +110,7 @@ class ConvGatedAttention(Mixer):
             self.proj(x, proj)
         qkv = ctx.ws.rows("cga_qkv", T, (self.nh + 2 * self.nkv) * hd, self.dtype)
         # the convolution writes heads at the common size hd, the surplus columns zero
-        self.conv.run(proj, 0, ctx, state, qkv, [(0, self.nh + self.nkv, self.dk, 0, hd),
-                                                 (self.nq + self.nk, self.nkv, self.dv, (self.nh + self.nkv) * hd, hd)])
+        self.conv.run(proj, 0, ctx, state, qkv, (self.nh + self.nkv, self.dk, self.nkv, self.dv, hd))
         pos = self.position
         ops.rope_store(qkv, ctx.tok_pos, ctx.tok_entry, pages.block_table, pages.storage if pages.writable else None,
                        pages.page_size, self.nh, self.nkv, hd, pos.rot_dim, pos.inv_freq, pos.mscale)

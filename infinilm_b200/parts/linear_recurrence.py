@@ -154,7 +154,7 @@ class GatedDeltaRule(_FusableEnds, Mixer):
         T, nqk, nv, nh = x.shape[0], self.nqk, self.nv, self.nh
         proj = self._project(x, ctx.ws.rows("gdr_proj", T, self.n_proj_pad, torch.float32))
         qkv = ctx.ws.rows("gdr_qkv", T, self.n_conv, torch.float32)
-        self.conv.run(proj, 0, ctx, conv_state, qkv, [(0, 1, self.n_conv, 0, self.n_conv)], act=1)
+        self.conv.run(proj, 0, ctx, conv_state, qkv, (1, self.n_conv, self.n_conv), act=1)
         beta = ctx.ws.rows("gdr_beta", T, nh, torch.float32)
         gdec = ctx.ws.rows("gdr_decay", T, nh, torch.float32)
         ops.delta_prep(qkv, 0, nqk, self.ng, self.dk, self.dk ** -0.5, self.unit_eps, proj, self.n_conv, self.n_conv + nh,

@@ -34,13 +34,20 @@ class ShortConv:
             raise ValueError(f"short convolution: weights {tuple(w.shape)} != {(self.channels, self.taps)}")
         self.weight = w
 
-    def run(self, x: torch.Tensor, x_off: int, ctx, state, out: torch.Tensor, segments: List[Tuple[int, int, int, int]], act: int = 0) -> None:
-        """Convolves channels [x_off, x_off + channels) of `x`. `segments`: (first channel, number of segments, columns
-        of a segment, first output column, columns it is written as - the surplus zero) per run of equal segments,
-        given as (ch0, n_seg, seg_in, out_off, seg_out). Then leaves the state of the step's end in the write slots."""
-        for ch0, n_seg, seg_in, out_off, seg_out in segments:
-            ops.short_conv(x, x_off + ch0, self.weight[ch0: ch0 + n_seg * seg_in], state.storage, ch0, state.read_slots,
-                           ctx.tok_entry, ctx.entry_qstart, out, out_off, n_seg, seg_in, seg_out, act)
-        if state.writable:
-            ops.short_conv_state(x, x_off, self.channels, self.taps, state.storage, 0, state.read_slots, state.write_slots,
-                                 ctx.entry_qstart, ctx.n_entries)
+    def run(self, x: torch.Tensor, x_off: int, ctx, state, out: torch.Tensor, segments: Tuple, act: int = 0) -> None:
+        """Convolves channels [x_off, x_off + channels) of `x` into `out` from column 0: `segments` is (n_seg, seg_in, seg_out)
+        or (n_seg, seg_in, n_seg2, seg_in2, seg_out) - that many segments of seg_in channels (then n_seg2 of seg_in2), each
+        written seg_out columns wide, the surplus zero. Then leaves the state of the step's end in the write slots: for the
+        single tokens the convolution kernel does it itself, for the portions behind them a second kernel."""
+        if len(segments) == 3:
+            n1, s1, n2, s2, so = segments[0], segments[1], 0, 0, segments[2]
+        else:
+            n1, s1, n2, s2, so = segments
+        if n1 * s1 + n2 * s2 != self.channels:
+            raise ValueError("short convolution: the segments do not add up to the channels")
+        wr = state.write_slots if state.writable else None
+        ops.short_conv(x, x_off, self.weight, state.storage, 0, state.read_slots, ctx.tok_entry, ctx.entry_qstart, out, 0, n1, s1, so, act,
+                       n_seg2=n2, seg_in2=s2, write_slots=wr)
+        if wr is not None and ctx.n_entries > ctx.n_decode:
+            ops.short_conv_state(x, x_off, self.channels, self.taps, state.storage, 0, state.read_slots, wr, ctx.entry_qstart,
+                                 ctx.n_entries - ctx.n_decode, first_entry=ctx.n_decode)

@@ -25,9 +25,10 @@ def _step_arrays(lens, dev):
     return _i32(qstart, dev), _i32(tok_entry, dev)
 
 
+@pytest.mark.parametrize("fused_state", [False, True])
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_short_conv_in_portions_with_state(cuda_device, taps, dtype):
+def test_short_conv_in_portions_with_state(cuda_device, taps, dtype, fused_state):
     from infinilm_b200 import ops
     dev = cuda_device
     torch.manual_seed(taps)
@@ -38,7 +39,7 @@ def test_short_conv_in_portions_with_state(cuda_device, taps, dtype):
     state = torch.zeros(5, max(taps - 1, 1), C, device=dev)
     state[4] = 7.0                                # a slot that an earlier request left dirty: slot 3's first step reads slot 0 instead
     # steps: (slot, tokens) lists; a request's first step reads the zero slot
-    plan = [[(1, 5), (2, 2)], [(1, 1), (2, 1), (3, 1)], [(1, 2), (2, 6)], [(1, 29)]]
+    plan = [[(1, 5), (2, 2)], [(1, 1), (2, 1), (3, 1)], [(1, 2), (2, 6)], [(1, 1)], [(1, 28)]]
     done = {s: 0 for s in seqs}
     got = {s: [] for s in seqs}
     for step in plan:
@@ -48,8 +49,15 @@ def test_short_conv_in_portions_with_state(cuda_device, taps, dtype):
         rd = _i32([0 if done[s] == 0 else s for s, _ in step], dev)
         wr = _i32([s for s, _ in step], dev)
         out = torch.full((x.shape[0], 4 * seg_out + 3), 5.0, dtype=dtype, device=dev)
-        ops.short_conv(x, 0, w.to(dev), state, 0, rd, tok_entry, qstart, out, 3, C // seg_in, seg_in, seg_out, 0)
-        ops.short_conv_state(x, 0, C, taps, state, 0, rd, wr, qstart, len(step))
+        if fused_state:                           # as a step runs it: single tokens first, their state moved on by the convolution itself
+            n_single = sum(1 for _, n in step if n == 1)
+            assert all(n == 1 for _, n in step[:n_single]) and all(n > 1 for _, n in step[n_single:])
+            ops.short_conv(x, 0, w.to(dev), state, 0, rd, tok_entry, qstart, out, 3, C // seg_in // 2, seg_in, seg_out, 0,
+                           n_seg2=C // seg_in - C // seg_in // 2, seg_in2=seg_in, write_slots=wr)
+            ops.short_conv_state(x, 0, C, taps, state, 0, rd, wr, qstart, len(step) - n_single, first_entry=n_single)
+        else:
+            ops.short_conv(x, 0, w.to(dev), state, 0, rd, tok_entry, qstart, out, 3, C // seg_in, seg_in, seg_out, 0)
+            ops.short_conv_state(x, 0, C, taps, state, 0, rd, wr, qstart, len(step))
         o = out[:, 3:].float().cpu().view(-1, C // seg_in, seg_out)
         assert float(o[:, :, seg_in:].abs().max()) == 0.0 and float(out[:, :3].float().min()) == 5.0
         r = 0

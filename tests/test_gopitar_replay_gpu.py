@@ -133,13 +133,15 @@ def test_decode_steps_with_norms_in_the_products(cuda_device, name, seed, monkey
     for fused in (True, False):
         monkeypatch.setattr(PreNormResidual, "FUSE_NORM", fused)
         eng = _engine(raw, w, "bfloat16")
-        assert all(b.mixer.fuses_tail(4) and b.mixer.accepts_normed(4) and not b.mixer.fuses_tail(40) for b in eng.model.blocks)
+        assert not any(b.mixer.fuses_tail(40) or b.mixer.accepts_normed(40) for b in eng.model.blocks)
+        can = [b.mixer.fuses_tail(4) and b.ffn is not None for b in eng.model.blocks]      # (sizes that are no multiple of 8 keep the kernels)
+        assert name == "d" or all(c or b.ffn is None for c, b in zip(can, eng.model.blocks))
         calls = []
         real = ops.gemm_skinny_resid
         monkeypatch.setattr(ops, "gemm_skinny_resid", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
         outs[fused] = _run_cut(eng, ids, [40, 3] + [1] * 17)
         monkeypatch.setattr(ops, "gemm_skinny_resid", real)
-        assert bool(calls) == fused
+        assert bool(calls) == (fused and any(can))
         eng.synchronize()
     ref = _oracle(name, seed, ids)
     _check(outs[True], ref, "bfloat16", f"{name} fused")
