@@ -92,7 +92,7 @@ def _scan(ops, mode, q, k, v, H, G, d, dv, decay, beta, g, state, slot, first, d
     return out
 
 
-@pytest.mark.parametrize("H,G,d,dv", [(2, 2, 32, 32), (3, 1, 8, 40), (4, 2, 64, 128), (1, 1, 20, 12), (2, 1, 128, 64), (1, 1, 256, 36), (2, 2, 136, 8)])
+@pytest.mark.parametrize("H,G,d,dv", [(2, 2, 32, 32), (3, 1, 8, 40), (4, 2, 64, 128), (1, 1, 20, 12), (2, 1, 128, 64), (1, 1, 256, 36), (2, 2, 136, 8), (2, 1, 10, 6), (1, 1, 50, 33)])
 def test_decayed_sum_whole_and_token_by_token(cuda_device, scan_kernel, H, G, d, dv):
     from infinilm_b200 import ops
     dev = cuda_device
@@ -123,7 +123,7 @@ def test_decayed_sum_whole_and_token_by_token(cuda_device, scan_kernel, H, G, d,
         assert float((moved[-1, :dv] - whole[-1, :dv]).abs().max()) > 1e-3 * scale
 
 
-@pytest.mark.parametrize("H,G,d,dv", [(2, 1, 32, 64), (6, 2, 8, 12), (3, 3, 24, 16), (2, 2, 128, 128), (1, 1, 40, 32), (1, 1, 200, 130), (2, 1, 4, 4)])
+@pytest.mark.parametrize("H,G,d,dv", [(2, 1, 32, 64), (6, 2, 8, 12), (3, 3, 24, 16), (2, 2, 128, 128), (1, 1, 40, 32), (1, 1, 200, 130), (2, 1, 4, 4), (4, 2, 10, 6), (1, 1, 70, 33)])
 def test_delta_rule_with_its_preparation(cuda_device, scan_kernel, H, G, d, dv):
     from infinilm_b200 import ops
     dev = cuda_device
@@ -196,7 +196,7 @@ def test_scan_of_a_batch_equals_each_alone(cuda_device, scan_kernel):
         a += n
 
 
-@pytest.mark.parametrize("H,d,dv", [(2, 32, 32), (3, 8, 40), (1, 128, 64), (2, 20, 12)])
+@pytest.mark.parametrize("H,d,dv", [(2, 32, 32), (3, 8, 40), (1, 128, 64), (2, 20, 12), (2, 10, 6), (1, 250, 9)])
 def test_decayed_sum_in_segments(cuda_device, H, d, dv):
     """Long portions walked in segments that run at once, with the second pass that adds each segment's start: several
     entries of unequal length (one segment, an exact multiple, a ragged end), from states that hold something, against
