@@ -630,7 +630,8 @@ IL_EXPORT int il_group_norm_gate(const float* x, int ldx, const void* w, int w_k
                                  cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (group <= 0 || n_groups <= 0 || n_w <= 0) return IL_BAD_ARG;
-    const int threads = group >= 256 ? 256 : group >= 128 ? 128 : 64;
+    // (a group of thousands of columns is one block: many threads, two to four columns each, keep its two passes short)
+    const int threads = group >= 2048 ? 1024 : group >= 1024 ? 512 : group >= 256 ? 256 : group >= 128 ? 128 : 64;
     const dim3 grid(T, n_groups);
 #define GN_ARGS x, ldx, w, w_kind, n_w, eps
     if (gate_kind == IL_F32 && out_kind == IL_F32)
