@@ -372,7 +372,7 @@ class OpTimer:
 
 
 def run_designs(args) -> int:
-    """Prefill tok/s (one prompt of 2,048 tokens) and decode tok/s (batch 8 and 64 over 2,048 cached tokens each, replayed as
+    """Prefill tok/s (one prompt of 2,048 tokens, launched eagerly and replayed as a graph) and decode tok/s (batch 8 and 64 over 2,048 cached tokens each, replayed as
     graphs) of the Nirozen design at layer sizes of real models, random weights, bfloat16, beside the dense GQA model of
     equal width, depth, heads and active feed-forward width; and for one eager step of each kind the time of every kernel
     (CUDA events around each launch). Prints one JSON line per size."""
@@ -450,6 +450,21 @@ def run_designs(args) -> int:
                 ms = a.elapsed_time(b) / n
                 res[f"decode_b{b_}_ms"] = round(ms, 4)
                 res[f"decode_b{b_}_tok_s"] = round(b_ / ms * 1e3)
+            # the prompt step once more, replayed as a graph (its shape has come back often enough by the fifth time): what
+            # the GPU needs for it without the host's share of some seventy launches
+            ts = []
+            for i in range(9):
+                s = eng.open(("g", i))
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                eng.step([StepEntry(s, prompts[i % B], [P - 1])])
+                b.record()
+                torch.cuda.synchronize()
+                eng.close(s)
+                ts.append(a.elapsed_time(b))
+            res["prefill_replayed_ms"] = round(statistics.median(ts[-4:]), 3)
+            res["prefill_replayed_tok_s"] = round(P / statistics.median(ts[-4:]) * 1e3)
+            res["prompt_steps_replayed"] = eng.runner.portion_replays
             eng.synchronize()
             rec[which] = res
             del eng, seqs

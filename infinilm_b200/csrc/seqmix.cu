@@ -29,20 +29,24 @@ __global__ void short_conv_kernel(const TI* __restrict__ x, int ldx, int x_off, 
                                   const int* __restrict__ read_slots, const int* __restrict__ write_slots, const int* __restrict__ tok_entry,
                                   const int* __restrict__ qstart, TO* __restrict__ out, int ldo, int out_off, int n_seg, int seg_in,
                                   int n_seg2, int seg_in2, int seg_out, int act, int T) {
-    // columns: n_seg segments of seg_in channels, then n_seg2 of seg_in2, every segment written seg_out wide
+    // columns: n_seg segments of seg_in channels, then n_seg2 of seg_in2, every segment written seg_out wide.
+    // blockIdx.y walks the tokens, the block's threads consecutive columns.
     const int cols = (n_seg + n_seg2) * seg_out;
-    const size_t total = (size_t)T * cols;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int t = (int)(idx / cols), oc = (int)(idx - (size_t)t * cols);
-        const int seg = oc / seg_out, within = oc - seg * seg_out;
-        const bool second = seg >= n_seg;
-        const int width = second ? seg_in2 : seg_in;
+    const int oc = blockIdx.x * blockDim.x + threadIdx.x;
+    if (oc >= cols) return;
+    const int seg = oc / seg_out, within = oc - seg * seg_out;
+    const bool second = seg >= n_seg;
+    const int width = second ? seg_in2 : seg_in;
+    const int ch = second ? n_seg * seg_in + (seg - n_seg) * seg_in2 + within : seg * seg_in + within;
+    float wt[SM_MAX_TAPS];
+    if (within < width)
+        for (int j = 0; j < taps; ++j) wt[j] = w[(size_t)ch * taps + j];
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
         TO* o = out + (size_t)t * ldo + out_off + oc;
         if (within >= width) {
             *o = il_from_f<TO>(0.f);
             continue;
         }
-        const int ch = second ? n_seg * seg_in + (seg - n_seg) * seg_in2 + within : seg * seg_in + within;
         const int e = tok_entry[t];
         const int first = qstart[e], local = t - first;
         const bool alone = write_slots && qstart[e + 1] - first == 1;     // the entry's only token: this thread also moves the state on
@@ -51,13 +55,67 @@ __global__ void short_conv_kernel(const TI* __restrict__ x, int ldx, int x_off, 
         for (int j = 0; j < taps; ++j) {
             const int s = local - (taps - 1) + j;
             const float u = s >= 0 ? il_to_f(x[(size_t)(t - local + s) * ldx + x_off + ch]) : st[(size_t)(taps - 1 + s) * st_ld];
-            acc = fmaf(w[(size_t)ch * taps + j], u, acc);
+            acc = fmaf(wt[j], u, acc);
             keep[j] = u;
         }
         *o = il_from_f<TO>(act == 1 ? sm_silu(acc) : acc);
         if (alone) {                              // nobody else reads this entry's state for this channel: safe in place
             float* wr = state + (size_t)write_slots[e] * slot_stride + st_off + ch;
             for (int j = 1; j < taps; ++j) wr[(size_t)(j - 1) * st_ld] = keep[j];
+        }
+    }
+}
+
+// The same with the taps known at compile time and a thread walking TT consecutive tokens of its column: the last
+// taps-1 inputs ride along in registers (rows of an entry are consecutive, so the row before a token is its predecessor
+// whenever it has one in this step), each input is read once, nothing lives in local memory.
+template <typename TI, typename TO, int TAPS, int TT>
+__global__ void short_conv_tile_kernel(const TI* __restrict__ x, int ldx, int x_off, const float* __restrict__ w,
+                                       float* state, size_t slot_stride, int st_off, int st_ld,
+                                       const int* __restrict__ read_slots, const int* __restrict__ write_slots, const int* __restrict__ tok_entry,
+                                       const int* __restrict__ qstart, TO* __restrict__ out, int ldo, int out_off, int n_seg, int seg_in,
+                                       int n_seg2, int seg_in2, int seg_out, int act, int T) {
+    const int cols = (n_seg + n_seg2) * seg_out;
+    const int oc = blockIdx.x * blockDim.x + threadIdx.x;
+    if (oc >= cols) return;
+    const int seg = oc / seg_out, within = oc - seg * seg_out;
+    const bool second = seg >= n_seg;
+    const int width = second ? seg_in2 : seg_in;
+    const int t0 = blockIdx.y * TT;
+    if (within >= width) {
+        for (int i = 0; i < TT && t0 + i < T; ++i) out[(size_t)(t0 + i) * ldo + out_off + oc] = il_from_f<TO>(0.f);
+        return;
+    }
+    const int ch = second ? n_seg * seg_in + (seg - n_seg) * seg_in2 + within : seg * seg_in + within;
+    float wt[TAPS], win[TAPS > 1 ? TAPS - 1 : 1];         // win[j]: the input j + 1 rows back
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wt[j] = w[(size_t)ch * TAPS + j];
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) win[j] = t0 - 1 - j >= 0 ? il_to_f(x[(size_t)(t0 - 1 - j) * ldx + x_off + ch]) : 0.f;
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+        const int t = t0 + i;
+        if (t < T) {
+            const float cur = il_to_f(x[(size_t)t * ldx + x_off + ch]);
+            const int e = tok_entry[t];
+            const int first = qstart[e], local = t - first;
+            const float* st = state + (size_t)read_slots[e] * slot_stride + st_off + ch;
+            float u[TAPS];                        // u[j]: the input j tokens back in the sequence
+            u[0] = cur;
+#pragma unroll
+            for (int j = 1; j < TAPS; ++j) u[j] = local - j >= 0 ? win[j - 1] : st[(size_t)(TAPS - 1 + local - j) * st_ld];
+            float acc = 0.f;
+#pragma unroll
+            for (int j = TAPS - 1; j >= 0; --j) acc = fmaf(wt[TAPS - 1 - j], u[j], acc);      // oldest first, as the plain kernel sums
+            out[(size_t)t * ldo + out_off + oc] = il_from_f<TO>(act == 1 ? sm_silu(acc) : acc);
+            if (write_slots && qstart[e + 1] - first == 1) {       // the entry's only token: this thread also moves the state on
+                float* wr = state + (size_t)write_slots[e] * slot_stride + st_off + ch;
+#pragma unroll
+                for (int j = 0; j < TAPS - 1; ++j) wr[(size_t)(TAPS - 2 - j) * st_ld] = u[j];
+            }
+#pragma unroll
+            for (int j = TAPS - 2; j > 0; --j) win[j] = win[j - 1];
+            if (TAPS > 1) win[0] = cur;
         }
     }
 }
@@ -97,7 +155,28 @@ IL_EXPORT int il_short_conv(const void* x, int x_kind, int ldx, int x_off, const
     if (T <= 0 || n_seg <= 0) return IL_OK;
     if (taps < 1 || taps > SM_MAX_TAPS || seg_in <= 0 || seg_out < seg_in || n_seg2 < 0 || (n_seg2 > 0 && (seg_in2 <= 0 || seg_out < seg_in2)))
         return IL_BAD_ARG;
-    const int grid = sm_grid((size_t)T * (n_seg + n_seg2) * seg_out, 256);
+    const int cols_all = (n_seg + n_seg2) * seg_out;
+    if (taps <= 8) {                              // the usual few taps: the tiled form
+        constexpr int TT = 8;
+        const dim3 tgrid((cols_all + 127) / 128, (T + TT - 1) / TT);
+#define SC_TILE(TI_, TO_, TAPS_)                                                                                              \
+        short_conv_tile_kernel<TI_, TO_, TAPS_, TT><<<tgrid, 128, 0, stream>>>((const TI_*)x, ldx, x_off, w, state, (size_t)slot_stride, st_off, \
+            st_ld, read_slots, write_slots, tok_entry, qstart, (TO_*)out, ldo, out_off, n_seg, seg_in, n_seg2, seg_in2, seg_out, act, T)
+#define SC_TAPS(TI_, TO_)                                                                                  \
+        switch (taps) {                                                                                    \
+            case 1: SC_TILE(TI_, TO_, 1); break; case 2: SC_TILE(TI_, TO_, 2); break;                      \
+            case 3: SC_TILE(TI_, TO_, 3); break; case 4: SC_TILE(TI_, TO_, 4); break;                      \
+            case 5: SC_TILE(TI_, TO_, 5); break; case 6: SC_TILE(TI_, TO_, 6); break;                      \
+            case 7: SC_TILE(TI_, TO_, 7); break; default: SC_TILE(TI_, TO_, 8); break;                     \
+        }
+        if (x_kind == IL_F32 && out_kind == IL_F32) { SC_TAPS(float, float) }
+        else if (x_kind == IL_BF16 && out_kind == IL_F32) { SC_TAPS(__nv_bfloat16, float) }
+        else if (x_kind == IL_BF16 && out_kind == IL_BF16) { SC_TAPS(__nv_bfloat16, __nv_bfloat16) }
+        else return IL_BAD_ARG;
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
+    const dim3 grid((cols_all + 255) / 256, T < 32768 ? T : 32768);
 #define SC_ARGS ldx, x_off, w, taps, state, (size_t)slot_stride, st_off, st_ld, read_slots, write_slots, tok_entry, qstart
 #define SC_TAIL ldo, out_off, n_seg, seg_in, n_seg2, seg_in2, seg_out, act, T
     if (x_kind == IL_F32 && out_kind == IL_F32)
@@ -519,18 +598,18 @@ static void sr_launch(dim3 grid, size_t smem, cudaStream_t stream, const float* 
 }
 
 // In place: x[t, c] = silu(x[t, c]) for the first `cols` columns of float32 rows (the recurrences' inputs, as a pass of its own).
-__global__ void silu_cols_kernel(float* x, int ld, int cols, size_t total) {
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / cols;
-        float* p = x + t * ld + (idx - t * cols);
+__global__ void silu_cols_kernel(float* x, int ld, int cols, int T) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+        float* p = x + (size_t)t * ld + c;
         *p = sm_silu_fast(*p);
     }
 }
 
 IL_EXPORT int il_silu_cols(float* x, int ld, int cols, int T, cudaStream_t stream) {
     if (T <= 0 || cols <= 0) return IL_OK;
-    const size_t total = (size_t)T * cols;
-    silu_cols_kernel<<<sm_grid(total, 256), 256, 0, stream>>>(x, ld, cols, total);
+    silu_cols_kernel<<<dim3((cols + 255) / 256, T < 32768 ? T : 32768), 256, 0, stream>>>(x, ld, cols, T);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
@@ -651,11 +730,11 @@ IL_EXPORT int il_group_norm_gate(const float* x, int ldx, const void* w, int w_k
 // columns come out packed). Without a gate only the packing is done.
 template <typename TA>
 __global__ void head_gate_kernel(const TA* __restrict__ y, int ldy, int hd, const TA* __restrict__ gate, int ldg, int g_off,
-                                 TA* __restrict__ out, int ldo, int nh, int vdim, size_t total) {
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int per = nh * vdim;
-        const int t = (int)(idx / per), j = (int)(idx - (size_t)t * per);
-        const int h = j / vdim, c = j - h * vdim;
+                                 TA* __restrict__ out, int ldo, int nh, int vdim, int T) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;      // output column; blockIdx.y walks the tokens
+    if (j >= nh * vdim) return;
+    const int h = j / vdim, c = j - h * vdim;
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
         const float s = gate ? sm_sigmoid(il_to_f(gate[(size_t)t * ldg + g_off + h])) : 1.f;
         out[(size_t)t * ldo + j] = il_from_f<TA>(il_to_f(y[(size_t)t * ldy + h * hd + c]) * s);
     }
@@ -665,13 +744,12 @@ IL_EXPORT int il_head_gate(const void* y, int kind, int ldy, int hd, const void*
                            int vdim, int T, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (nh <= 0 || vdim <= 0 || vdim > hd) return IL_BAD_ARG;
-    const size_t total = (size_t)T * nh * vdim;
-    const int grid = sm_grid(total, 256);
+    const dim3 grid((nh * vdim + 255) / 256, T < 32768 ? T : 32768);
     if (kind == IL_F32)
-        head_gate_kernel<float><<<grid, 256, 0, stream>>>((const float*)y, ldy, hd, (const float*)gate, ldg, g_off, (float*)out, ldo, nh, vdim, total);
+        head_gate_kernel<float><<<grid, 256, 0, stream>>>((const float*)y, ldy, hd, (const float*)gate, ldg, g_off, (float*)out, ldo, nh, vdim, T);
     else if (kind == IL_BF16)
         head_gate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)y, ldy, hd, (const __nv_bfloat16*)gate, ldg, g_off,
-                                                                  (__nv_bfloat16*)out, ldo, nh, vdim, total);
+                                                                  (__nv_bfloat16*)out, ldo, nh, vdim, T);
     else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();
